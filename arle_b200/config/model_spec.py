@@ -37,6 +37,8 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
     ignored_tensors: Tuple[str, ...] = ()     # names a checkpoint may carry that the model does not read
     kind: str = "decoder"                     # the registered model class that is built from this spec
+    embed_scale: float = 1.0                  # the embedding row is multiplied by this
+    logit_cap: Optional[float] = None         # logits <- cap * tanh(logits / cap)
 
     def validate(self) -> None:
         if not self.blocks or not self.schedule:

@@ -32,9 +32,13 @@ def registered_architectures():
 
 
 def config_class_for(config_dict: dict) -> type:
+    """By the ``architectures`` list of config.json, or by its single ``architecture`` name."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if not archs or not isinstance(archs, list):
-        raise UnknownArchitecture("config.json has no 'architectures' list; known: " + ", ".join(registered_architectures()))
+        raise UnknownArchitecture("config.json has neither an 'architectures' list nor an 'architecture' name; known: "
+                                  + ", ".join(registered_architectures()))
     for a in archs:
         if a in _ARCHITECTURES:
             return _ARCHITECTURES[a]

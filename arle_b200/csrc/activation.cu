@@ -1,10 +1,15 @@
-// SwiGLU gate: out[t, i] = silu(gu[t, 2i]) * gu[t, 2i + 1], silu(g) = g / (1 + exp(-g)),
-// computed in float32 and rounded once.  gu is the [T, 2I] output of the packed
+// Gate of a gated feed-forward: out[t, i] = act(gu[t, 2i]) * gu[t, 2i + 1], computed in float32 and
+// rounded once.  act 0: silu(g) = g / (1 + exp(-g)) (SwiGLU); act 1: the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).  gu is the [T, 2I] output of the packed
 // gate/up projection, whose rows 2i and 2i + 1 are gate_i and up_i.
 #include "common.cuh"
 using namespace arle;
 
-template <typename T>
+__device__ __forceinline__ float gelu_tanh_f(float g) {
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
@@ -14,11 +19,12 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     const int i = (int)(idx - t * inter);
     const float g = to_f32(gu[t * 2 * (size_t)inter + 2 * i]);
     const float u = to_f32(gu[t * 2 * (size_t)inter + 2 * i + 1]);
-    out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    out[idx] = from_f32<T>((ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh_f(g)) * u);
   }
 }
 
 // Eight elements per thread and step for bfloat16 rows whose width is a multiple of 8.
+template <int ACT>
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
                                          size_t total8) {
   pdl_launch_dependents();
@@ -39,16 +45,18 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, _
       const float ga = __low2float(p0), gb = __low2float(p1);
       // fast exponential and division (a few ulp of float32, far below the bfloat16 rounding that follows):
       // with the exact ones the kernel was bound by arithmetic, not by memory
-      o2[k] = __floats2bfloat162_rn(__fdividef(ga, 1.0f + __expf(-ga)) * __high2float(p0),
-                                    __fdividef(gb, 1.0f + __expf(-gb)) * __high2float(p1));
+      if (ACT == 0)
+        o2[k] = __floats2bfloat162_rn(__fdividef(ga, 1.0f + __expf(-ga)) * __high2float(p0),
+                                      __fdividef(gb, 1.0f + __expf(-gb)) * __high2float(p1));
+      else
+        o2[k] = __floats2bfloat162_rn(gelu_tanh_f(ga) * __high2float(p0), gelu_tanh_f(gb) * __high2float(p1));
     }
     *reinterpret_cast<uint4*>(out + t * (size_t)inter + 8 * c) = o4;
   }
 }
 
-ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
-  if (num_tokens <= 0) return 0;
-  if (inter <= 0) return ARLE_E_BADARG;
+template <int ACT>
+static int act_mul_launch(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
   const size_t total = (size_t)num_tokens * inter;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
@@ -57,14 +65,27 @@ ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens,
     const size_t total8 = total / 8;
     size_t b8 = (total8 + threads - 1) / threads;
     if (b8 > 148 * 32) b8 = 148 * 32;
-    launch_kernel(silu_mul_bf16_vec_kernel, dim3((int)b8), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
+    launch_kernel(silu_mul_bf16_vec_kernel<ACT>, dim3((int)b8), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
     return launch_status();
   }
   if (dtype == 0)
-    launch_kernel(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, inter, total);
+    launch_kernel(silu_mul_kernel<float, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, inter, total);
   else if (dtype == 1)
-    launch_kernel(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    launch_kernel(silu_mul_kernel<__nv_bfloat16, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
   else
     return ARLE_E_BADARG;
   return launch_status();
+}
+
+ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (inter <= 0) return ARLE_E_BADARG;
+  return act_mul_launch<0>(gu, out, dtype, num_tokens, inter, s);
+}
+
+// act: 0 silu, 1 gelu (tanh form)
+ARLE_API int arle_act_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, int act, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (inter <= 0 || (act != 0 && act != 1)) return ARLE_E_BADARG;
+  return act == 0 ? act_mul_launch<0>(gu, out, dtype, num_tokens, inter, s) : act_mul_launch<1>(gu, out, dtype, num_tokens, inter, s);
 }

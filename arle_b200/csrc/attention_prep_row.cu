@@ -1,0 +1,114 @@
+// Preparation of queries and keys for an attention whose q/k norm runs over the whole
+// projected row (all heads at once) and whose values may be the keys as projected.
+//
+// Input row t of qk: [q heads (nq * hd) | k heads (nkv * hd) | ...] (row stride given).
+// One block per token:
+//   q: x <- x * rsqrt(mean over all nq*hd elements of x^2 + eps) * q_weight[e] (if q_weight),
+//      rotate, store in place;
+//   k: the same over the nkv*hd elements with k_weight, rotate, store into k_cache at the
+//      token's slot;
+//   v: with values_are_keys the row of k as projected (before norm and rotation) goes into
+//      v_cache unchanged; otherwise the v heads that follow the k heads in the row do.
+// Rotation, within the first rotary_dim elements of each head: pairing 0 turns element i with
+// i + rotary_dim/2 ("half split"), pairing 1 turns element 2i with 2i + 1 ("interleaved"); the
+// pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a) with a = position * inv_freq[i],
+// in float32 (sincosf).  Norm statistics and products are float32.
+// Cache layout: [page][kv_head][slot_in_page][head_dim]; slot_mapping[t] < 0: no store.
+#include "common.cuh"
+using namespace arle;
+
+template <typename T>
+__global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, const int* __restrict__ positions,
+                                          const int* __restrict__ slot_mapping, const float* __restrict__ q_weight,
+                                          const float* __restrict__ k_weight, float eps,
+                                          const float* __restrict__ inv_freq, int rotary_dim, int pairing,
+                                          int values_are_keys, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          int nq, int nkv, int hd, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];                 // (nq + nkv) * hd floats
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int nqe = nq * hd, nke = nkv * hd;
+  T* src = qk + (size_t)t * row_stride;
+  float sq = 0.f, sk = 0.f;
+  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
+    const float x = to_f32(src[e]);
+    row[e] = x;
+    if (e < nqe) sq += x * x; else sk += x * x;
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  const float inv_q = q_weight ? 1.0f / sqrtf(sq / (float)nqe + eps) : 1.0f;
+  const float inv_k = k_weight ? 1.0f / sqrtf(sk / (float)(nke > 0 ? nke : 1) + eps) : 1.0f;
+  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
+    if (e < nqe) {
+      if (q_weight) row[e] = row[e] * inv_q * q_weight[e];
+    } else if (k_weight) {
+      row[e] = row[e] * inv_k * k_weight[e - nqe];
+    }
+  }
+  __syncthreads();
+  const int slot = nkv > 0 ? slot_mapping[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
+  const float pos = (float)positions[t];
+  const int half = rotary_dim >> 1;
+  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
+    const int head = e / hd, d = e - head * hd;
+    float o = row[e];
+    if (d < rotary_dim) {
+      int i, partner;
+      bool first;
+      if (pairing == 0) {
+        first = d < half;
+        i = first ? d : d - half;
+        partner = first ? e + half : e - half;
+      } else {
+        first = (d & 1) == 0;
+        i = d >> 1;
+        partner = first ? e + 1 : e - 1;
+      }
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      o = first ? row[e] * cs - row[partner] * sn : row[e] * cs + row[partner] * sn;
+    }
+    if (e < nqe) {
+      src[e] = from_f32<T>(o);
+    } else if (slot >= 0) {
+      const int kvh = head - nq;
+      const size_t at = (((size_t)page * nkv + kvh) * page_size + off) * hd + d;
+      k_cache[at] = from_f32<T>(o);
+      v_cache[at] = values_are_keys ? src[e] : src[e + nke];
+    }
+  }
+}
+
+ARLE_API int arle_attention_prep_row(void* qk, int dtype, int row_stride, const int* positions, const int* slot_mapping,
+                                     const float* q_weight, const float* k_weight, float eps, const float* inv_freq,
+                                     int rotary_dim, int pairing, int values_are_keys, void* k_cache, void* v_cache, int nq,
+                                     int nkv, int hd, int page_size, int num_tokens, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (hd <= 0 || nq <= 0 || nkv < 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return ARLE_E_BADARG;
+  if (pairing != 0 && pairing != 1) return ARLE_E_BADARG;
+  if (rotary_dim > 0 && !inv_freq) return ARLE_E_BADARG;
+  if (nkv > 0 && (!slot_mapping || !k_cache || !v_cache)) return ARLE_E_BADARG;
+  const size_t smem = (size_t)(nq + nkv) * hd * sizeof(float);
+  if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
+  const int n = (nq + nkv) * hd;
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  if (dtype == 0) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_prep_row_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(attention_prep_row_kernel<float>, dim3(num_tokens), dim3(threads), smem, s, 1, (float*)qk, row_stride, positions,
+                  slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys, (float*)k_cache,
+                  (float*)v_cache, nq, nkv, hd, page_size);
+  } else if (dtype == 1) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(attention_prep_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(attention_prep_row_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), smem, s, 1, (__nv_bfloat16*)qk,
+                  row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys,
+                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, hd, page_size);
+  } else {
+    return ARLE_E_BADARG;
+  }
+  return launch_status();
+}

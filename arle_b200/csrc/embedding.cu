@@ -1,4 +1,4 @@
-// Token embedding: residual[t, :] = float32(table[ids[t], :]).
+// Token embedding: residual[t, :] = float32(table[ids[t], :]) * scale (scale 1 for most models).
 // A negative id is a placeholder for "the token this request sampled last": it is read
 // from last_token[slot_of_token[t]], which the sampling kernels write on the device, so
 // that a decode step can be launched before the host has seen the previous step's tokens.
@@ -12,7 +12,7 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab,
                                  int* __restrict__ err, const int* __restrict__ last_token,
-                                 const int* __restrict__ slot_of_token) {
+                                 const int* __restrict__ slot_of_token, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -25,13 +25,13 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 // Eight table elements per thread and step (16-byte loads of bfloat16 rows).
 __global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                           float* __restrict__ out, int hidden, int vocab, int* __restrict__ err,
-                                          const int* __restrict__ last_token, const int* __restrict__ slot_of_token) {
+                                          const int* __restrict__ last_token, const int* __restrict__ slot_of_token, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -45,14 +45,14 @@ __global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __n
     uint4 u = make_uint4(0, 0, 0, 0);
     if (!bad) u = row[c];
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-    o[2 * c] = make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
-    o[2 * c + 1] = make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]));
+    o[2 * c] = make_float4(__low2float(h[0]) * scale, __high2float(h[0]) * scale, __low2float(h[1]) * scale, __high2float(h[1]) * scale);
+    o[2 * c + 1] = make_float4(__low2float(h[2]) * scale, __high2float(h[2]) * scale, __low2float(h[3]) * scale, __high2float(h[3]) * scale);
   }
 }
 
 ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, float* out,
                             int num_tokens, int hidden, int vocab, int* err, const int* last_token,
-                            const int* slot_of_token, cudaStream_t s) {
+                            const int* slot_of_token, float scale, cudaStream_t s) {
   if (last_token && !slot_of_token) return ARLE_E_BADARG;
   if (num_tokens <= 0) return 0;
   if (hidden <= 0 || vocab <= 0) return ARLE_E_BADARG;
@@ -60,13 +60,13 @@ ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, 
   if (table_dtype == 1 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     int th = hidden / 8;
     th = th <= 32 ? 32 : (th <= 64 ? 64 : (th <= 128 ? 128 : (th <= 256 ? 256 : 512)));
-    launch_kernel(embedding_bf16_vec_kernel, dim3(num_tokens), dim3(th), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token);
+    launch_kernel(embedding_bf16_vec_kernel, dim3(num_tokens), dim3(th), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token, scale);
     return launch_status();
   }
   if (table_dtype == 0)
-    launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const float*)table, out, hidden, vocab, err, last_token, slot_of_token);
+    launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const float*)table, out, hidden, vocab, err, last_token, slot_of_token, scale);
   else if (table_dtype == 1)
-    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token);
+    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token, scale);
   else
     return ARLE_E_BADARG;
   return launch_status();

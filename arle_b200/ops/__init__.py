@@ -39,10 +39,18 @@ def add_launches(n: int) -> None:
 
 _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
-    "arle_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P],
+    "arle_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _F, _P],
     "arle_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "arle_residual_add": [_P, _P, _I, _I, _I, _P],
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "arle_act_mul": [_P, _P, _I, _I, _I, _I, _P],
+    "arle_attention_prep_row": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_head_gate": [_P, _I, _P, _I, _F, _P, _I, _I, _I, _I, _I, _P],
+    "arle_weighted_sum": [_P, _F, _P, _F, _P, _I, ctypes.c_longlong, _P],
+    "arle_logit_cap": [_P, _F, ctypes.c_longlong, _P],
+    "arle_gla_decay": [_P, _I, _I, _P, _P, _F, _P, _I, _I, _I, _P],
+    "arle_gla_scan": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "arle_gla_out": [_P, _P, _I, _I, _P, _F, _F, _P, _I, _I, _I, _I, _P],
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_rotary_angles": [_P, _P, _P, _I, _I, _P],
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -204,8 +212,8 @@ def _i32(t, name):
 
 # ------------------------------------------------------------------- embedding
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor = None,
-              last_token: torch.Tensor = None, slot_of_token: torch.Tensor = None) -> None:
-    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; out float32 [T, H].  With
+              last_token: torch.Tensor = None, slot_of_token: torch.Tensor = None, scale: float = 1.0) -> None:
+    """out[t, :] = float32(table[ids[t], :]) * scale.  ids int32 [T]; out float32 [T, H].  With
     ``last_token`` (int32, one entry per request slot) and ``slot_of_token`` (int32 [T]) a
     negative id stands for last_token[slot_of_token[t]], the token the request sampled last."""
     T, H = out.shape
@@ -220,7 +228,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: to
             raise KernelError("embedding: slot_of_token must name a slot for every token")
     _check(library().arle_embedding(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, table.shape[0],
                                     _ptr(err), _ptr(last_token), _ptr(slot_of_token) if last_token is not None else None,
-                                    _stream()), "embedding")
+                                    float(scale), _stream()), "embedding")
 
 
 # ------------------------------------------------------------------------ norm
@@ -759,6 +767,31 @@ def gated_gemm_fits(K: int) -> bool:
     return 16 * (K + 8) <= 85600
 
 
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[t, i] = act(gate_up[t, 2i]) * gate_up[t, 2i + 1] for ``activation`` "silu" or "gelu_tanh" (the tanh
+    form of gelu); float32 arithmetic, rounded once."""
+    T, I = out.shape
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"act_mul: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
+        raise KernelError("act_mul: gate_up must be contiguous [T, 2I] and out contiguous [T, I] of one type")
+    _check(library().arle_act_mul(_ptr(gate_up), _ptr(out), _dt(out), T, I, ACTIVATIONS[activation], _stream()), "act_mul")
+
+
+def gemm_act_mul(x, w: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """The first half of a gated feed-forward with the named activation on the gate.  "silu" takes the fused
+    kernels of ``gemm_silu_mul`` where the shapes allow them; other activations run the product and then the
+    gate kernel."""
+    if activation == "silu":
+        gemm_silu_mul(x, w, gate_up, out)
+        return
+    gemm(x, w, gate_up)
+    act_mul(gate_up, out, activation)
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i + 1]; gate_up [T, 2I], out [T, I]."""
     T, I = out.shape
@@ -812,3 +845,127 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out) -> N
         _i32(top_k, "top_k")
     _check(library().arle_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
                                  _ptr(min_p), _ptr(uniform), _ptr(scratch), _ptr(out), _stream()), "sample")
+
+
+# ------------------------------------------------- attention with a norm over the whole row
+ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
+
+
+def attention_prep_row(qk, positions, slot_mapping, q_weight, k_weight, eps: float, inv_freq, rotary_dim: int, pairing: str,
+                       values_are_keys: bool, k_cache, v_cache, nq: int, nkv: int, hd: int, page_size: int) -> None:
+    """RMSNorm of q and of k over their whole projected rows (weights float32 [nq*hd], [nkv*hd], or None: no
+    norm), rotation of the first ``rotary_dim`` elements of every head (``pairing`` "half": element i with
+    i + rotary_dim/2; "interleaved": 2i with 2i + 1), q stored in place on qk [T, >= (nq + nkv) hd], k into the
+    paged k_cache; v_cache gets the keys as projected (``values_are_keys``) or the v heads that follow the k
+    heads in the row.  nkv = 0: queries only, nothing stored."""
+    T = qk.shape[0]
+    need = (nq + (nkv if values_are_keys else 2 * nkv)) * hd
+    if qk.stride(1) != 1 or qk.shape[1] < need:
+        raise KernelError(f"attention_prep_row: qk must be [T, >= {need}] with unit inner stride")
+    if pairing not in ROTARY_PAIRINGS:
+        raise KernelError(f"attention_prep_row: pairing {pairing!r} (known: {', '.join(ROTARY_PAIRINGS)})")
+    for w_, n_ in ((q_weight, nq * hd), (k_weight, nkv * hd)):
+        if w_ is not None and (w_.dtype != torch.float32 or w_.numel() != n_ or not w_.is_contiguous()):
+            raise KernelError("attention_prep_row: norm weights must be contiguous float32 over the whole row")
+    if nkv > 0:
+        if k_cache.dtype != qk.dtype or v_cache.dtype != qk.dtype:
+            raise KernelError("attention_prep_row: cache type differs from activation type")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape or not (
+                k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise KernelError(f"attention_prep_row: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+        _i32(slot_mapping, "slot_mapping")
+    _i32(positions, "positions")
+    if rotary_dim and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("attention_prep_row: inv_freq must be float32 [rotary_dim / 2]")
+    _check(library().arle_attention_prep_row(
+        _ptr(qk), _dt(qk), qk.stride(0), _ptr(positions), _ptr(slot_mapping) if nkv else None, _ptr(q_weight), _ptr(k_weight),
+        float(eps), _ptr(inv_freq) if rotary_dim else None, int(rotary_dim), ROTARY_PAIRINGS[pairing], int(bool(values_are_keys)),
+        _ptr(k_cache) if nkv else None, _ptr(v_cache) if nkv else None, nq, nkv, hd, page_size, T, _stream()),
+        "attention_prep_row")
+
+
+def head_gate(x, gate, scale: float, out, heads: int, hd: int) -> None:
+    """out[t, h*hd + e] = x[t, h*hd + e] * sigmoid(gate[t, h]) * scale (gate None: no gate, a scaled copy).
+    x [T, heads*hd], gate [T, heads] and out [T, heads*hd] may be slices of wider rows (unit inner stride)."""
+    T = x.shape[0]
+    if (x.shape[1] != heads * hd or out.shape != (T, heads * hd) or x.dtype != out.dtype or x.stride(1) != 1
+            or out.stride(1) != 1 or (gate is not None and (gate.shape != (T, heads) or gate.dtype != out.dtype
+                                                            or gate.stride(1) != 1))):
+        raise KernelError(f"head_gate: shapes x {tuple(x.shape)} out {tuple(out.shape)} or the gate's do not fit")
+    _check(library().arle_head_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, float(scale),
+                                    _ptr(out), out.stride(0), _dt(out), T, heads, hd, _stream()), "head_gate")
+
+
+def weighted_sum(x, a: float, y, b: float, out) -> None:
+    """out = a * x + b * y (float32 arithmetic, rounded once); contiguous tensors of one shape and type."""
+    if x.shape != y.shape or x.shape != out.shape or x.dtype != y.dtype or x.dtype != out.dtype or not (
+            x.is_contiguous() and y.is_contiguous() and out.is_contiguous()):
+        raise KernelError("weighted_sum: x, y and out must be contiguous and of one shape and type")
+    _check(library().arle_weighted_sum(_ptr(x), float(a), _ptr(y), float(b), _ptr(out), _dt(out), x.numel(), _stream()),
+           "weighted_sum")
+
+
+def logit_cap(logits, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place; contiguous float32."""
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("logit_cap: logits must be contiguous float32")
+    _check(library().arle_logit_cap(_ptr(logits), float(cap), logits.numel(), _stream()), "logit_cap")
+
+
+# ------------------------------------------------------------ gated linear attention
+def gla_decay(low, w2, bias, tau: float, alpha) -> None:
+    """alpha[t, c] = sigmoid(bias[c] + sum_r low[t, r] * w2[c, r]) ^ (1 / tau), float32 [T, channels].  ``low``
+    [T, rank] in the activation type (a slice of a wider row is fine), w2 float32 [channels, rank], bias float32
+    [channels] or None."""
+    T, rank = low.shape
+    C = w2.shape[0]
+    if (w2.dtype != torch.float32 or w2.shape[1] != rank or not w2.is_contiguous() or alpha.dtype != torch.float32
+            or tuple(alpha.shape) != (T, C) or not alpha.is_contiguous() or low.stride(1) != 1):
+        raise KernelError(f"gla_decay: shapes low {tuple(low.shape)} w2 {tuple(w2.shape)} alpha {tuple(alpha.shape)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != C):
+        raise KernelError("gla_decay: bias must be float32 [channels]")
+    _check(library().arle_gla_decay(_ptr(low), _dt(low), low.stride(0), _ptr(w2), _ptr(bias), float(tau), _ptr(alpha), T, C,
+                                    rank, _stream()), "gla_decay")
+
+
+def gla_scan(q, k, v, alpha, state, q_indptr, state_slots, out, heads: int, dim: int, vdim: int, q_scale: float,
+             max_q_len: int) -> None:
+    """The recurrence S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_t * q_scale) over the tokens of every row of
+    the step (row r owns tokens q_indptr[r] .. q_indptr[r+1]-1), from and into state[state_slots[r]].
+    q, k [T, heads*dim] and v [T, heads*vdim]: slices of one wider buffer (same row stride, unit inner stride);
+    alpha float32 [T, heads*dim]; state float32 [slots, heads, vdim, dim] (a head's state transposed);
+    out float32 [T, heads*vdim]."""
+    T = q.shape[0]
+    R = state_slots.numel()
+    if (q.shape != (T, heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or q.dtype != k.dtype
+            or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1
+            or q.stride(0) != k.stride(0) or q.stride(0) != v.stride(0)):
+        raise KernelError("gla_scan: q, k, v must be slices of one buffer: [T, heads*dim], [T, heads*dim], [T, heads*vdim]")
+    if alpha.dtype != torch.float32 or tuple(alpha.shape) != (T, heads * dim) or not alpha.is_contiguous():
+        raise KernelError("gla_scan: alpha must be contiguous float32 [T, heads*dim]")
+    if (state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, vdim, dim) or not state.is_contiguous()):
+        raise KernelError(f"gla_scan: state {tuple(state.shape)} is not float32 [slots, {heads}, {vdim}, {dim}]")
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, heads * vdim) or not out.is_contiguous():
+        raise KernelError("gla_scan: out must be contiguous float32 [T, heads*vdim]")
+    _i32(q_indptr, "q_indptr"), _i32(state_slots, "state_slots")
+    if q_indptr.numel() != R + 1:
+        raise KernelError("gla_scan: q_indptr must have one entry more than state_slots")
+    _check(library().arle_gla_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), _ptr(alpha), _ptr(state), _ptr(q_indptr),
+                                   _ptr(state_slots), _ptr(out), R, heads, dim, vdim, float(q_scale), int(max_q_len), _stream()),
+           "gla_scan")
+
+
+def gla_out(o, gate, weight, eps: float, scale: float, out, heads: int, vdim: int) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]) * scale.
+    o float32 [T, heads*vdim] contiguous; gate (activation type, or None) and out may be slices of wider rows;
+    weight float32 [vdim] or None."""
+    T = o.shape[0]
+    if o.dtype != torch.float32 or tuple(o.shape) != (T, heads * vdim) or not o.is_contiguous():
+        raise KernelError("gla_out: o must be contiguous float32 [T, heads*vdim]")
+    if out.shape != o.shape or out.stride(1) != 1 or (gate is not None and (gate.shape != o.shape or gate.stride(1) != 1
+                                                                          or gate.dtype != out.dtype)):
+        raise KernelError("gla_out: gate and out must be [T, heads*vdim] of one type with unit inner stride")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != vdim):
+        raise KernelError("gla_out: weight must be float32 [vdim]")
+    _check(library().arle_gla_out(_ptr(o), _ptr(gate), _dt(out), gate.stride(0) if gate is not None else 0, _ptr(weight),
+                                  float(eps), float(scale), _ptr(out), out.stride(0), T, heads, vdim, _stream()), "gla_out")

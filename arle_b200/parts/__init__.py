@@ -1,13 +1,16 @@
 from .attention import Attention, AttentionSpec
 from .base import Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, StateNeed, WeightDecl
 from .block import PreNormBlock, PreNormBlockSpec
+from .linear_attention import GatedLinearAttention, GatedLinearAttentionSpec
 from .mlp import GatedMlp, GatedMlpSpec
 from .model import DecoderModel, ResidualStream, declared_weights
 from .norm import RmsNorm, RmsNormSpec
+from .parallel import ParallelBlock, ParallelBlockSpec, ParallelMixer, ParallelMixerSpec
 from .registry import build_model, build_part, register_model, register_part, registered_models, registered_parts
 from .rotary import Rotary, RotarySpec
 
 __all__ = ["Attention", "AttentionSpec", "Block", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part",
            "PositionEncoding", "StateNeed", "WeightDecl", "PreNormBlock", "PreNormBlockSpec", "GatedMlp",
-           "GatedMlpSpec", "DecoderModel", "ResidualStream", "declared_weights", "RmsNorm", "RmsNormSpec",
+           "GatedMlpSpec", "GatedLinearAttention", "GatedLinearAttentionSpec", "ParallelBlock", "ParallelBlockSpec",
+           "ParallelMixer", "ParallelMixerSpec", "DecoderModel", "ResidualStream", "declared_weights", "RmsNorm", "RmsNormSpec",
            "build_model", "build_part", "register_model", "register_part", "registered_models", "registered_parts", "Rotary", "RotarySpec"]

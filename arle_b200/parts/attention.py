@@ -1,16 +1,25 @@
-"""Grouped-query attention over the paged cache, with optional per-head RMSNorm
-of q and k, an optional rotary position encoding and an optional key window.
+"""Grouped-query attention over the paged cache, with an optional RMSNorm of q and k
+(per head, or over the whole projected row), an optional rotary position encoding, an
+optional key window, values that are projected or are the keys as projected, and an
+optional sigmoid gate per head on the output.
 
 Order of operations (infer/src/model/qwen3/prefill.rs:652-722): q/k/v projections
 without bias -> per-head norm of q and k -> rotation -> k, v into the cache ->
 causal attention, query head h reading kv head h // (num_heads / num_kv_heads)
 -> output projection.  The three input projections are packed into one matrix at
 load, so a step runs one product for them.
+
+Variants, each a field of the spec: ``qk_norm`` "row" norms q (and k) over all heads at once
+with a weight of the row's size; ``values`` "keys" has no value projection, the value of a key
+is its row of W_k x before norm and rotation (kept in the cache's second stream);
+``head_gate`` multiplies head h's output by sigmoid(W_g x)_h before the output projection
+(W_g's rows ride in the packed input projection); the position encoding's ``pairing`` chooses
+which elements turn together.  ``names`` gives the tensors' names after the prefix.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import ClassVar, Optional
+from typing import ClassVar, Optional, Tuple
 
 import torch
 
@@ -30,7 +39,15 @@ class AttentionSpec:
     qk_norm_eps: Optional[float]    # None: no per-head norm
     position: Optional[object]      # a position-encoding spec or None
     window: Optional[int] = None    # None: all keys; W: keys p-W+1 .. p
+    qk_norm: str = "head"           # "head": per head, weight [head_dim]; "row": over all heads, weight [heads*head_dim]
+    values: str = "projected"       # "projected": W_v x; "keys": the keys as projected
+    head_gate: bool = False         # head h's output times sigmoid(W_g x)_h
+    names: Optional[Tuple[Tuple[str, str], ...]] = None    # (role, name after the prefix); see DEFAULT_NAMES
     kind: ClassVar[str] = "attention"
+
+
+DEFAULT_NAMES = (("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"), ("o", "o_proj.weight"),
+                 ("q_norm", "q_norm.weight"), ("k_norm", "k_norm.weight"), ("gate", "g_proj.weight"))
 
 
 class Attention(Mixer):
@@ -41,33 +58,55 @@ class Attention(Mixer):
             raise ValueError(f"head_dim {spec.head_dim} not supported (even, at most 256)")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("window must be positive")
+        if spec.qk_norm not in ("head", "row") or spec.values not in ("projected", "keys"):
+            raise ValueError(f"attention: qk_norm {spec.qk_norm!r} / values {spec.values!r} not known")
         self.spec = spec
         self.position = build_part(spec.position) if spec.position is not None else None
+        self.pairing = getattr(self.position, "pairing", "half")
+        # the form the first kernels of this package were written for; everything else takes the general preparation
+        self.plain_form = (spec.qk_norm == "head" and spec.values == "projected" and not spec.head_gate
+                           and self.pairing == "half")
+        if not self.plain_form and spec.qk_norm == "head" and spec.qk_norm_eps is not None:
+            raise ValueError("attention: a per-head q/k norm goes with half-split rotation, projected values and no gate")
+        self.names = dict(DEFAULT_NAMES)
+        self.names.update(dict(spec.names or ()))
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.gate_at = None             # column of the packed projection where the gate numbers start
 
     # ---------------------------------------------------------------- weights
+    def _name(self, role: str) -> str:
+        return self.spec.prefix + self.names[role]
+
     def weight_decls(self):
-        s, p = self.spec, self.spec.prefix
+        s = self.spec
         dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        decls = [WeightDecl(p + "q_proj.weight", (dq, s.hidden_size)),
-                 WeightDecl(p + "k_proj.weight", (dkv, s.hidden_size)),
-                 WeightDecl(p + "v_proj.weight", (dkv, s.hidden_size)),
-                 WeightDecl(p + "o_proj.weight", (s.hidden_size, dq))]
+        decls = [WeightDecl(self._name("q"), (dq, s.hidden_size)), WeightDecl(self._name("k"), (dkv, s.hidden_size))]
+        if s.values == "projected":
+            decls.append(WeightDecl(self._name("v"), (dkv, s.hidden_size)))
+        decls.append(WeightDecl(self._name("o"), (s.hidden_size, dq)))
         if s.qk_norm_eps is not None:
-            decls += [WeightDecl(p + "q_norm.weight", (s.head_dim,), init="gain"),
-                      WeightDecl(p + "k_norm.weight", (s.head_dim,), init="gain")]
+            nq_, nk_ = ((s.head_dim,), (s.head_dim,)) if s.qk_norm == "head" else ((dq,), (dkv,))
+            decls += [WeightDecl(self._name("q_norm"), nq_, init="gain"), WeightDecl(self._name("k_norm"), nk_, init="gain")]
+        if s.head_gate:
+            decls.append(WeightDecl(self._name("gate"), (s.num_heads, s.hidden_size)))
         return tuple(decls)
 
     def load(self, tensors, dtype, device):
-        s, p = self.spec, self.spec.prefix
-        mats = [tensors[p + n + "_proj.weight"] for n in ("q", "k", "v")]
+        s = self.spec
+        mats = [tensors[self._name(n)] for n in (("q", "k", "v") if s.values == "projected" else ("q", "k"))]
+        if s.head_gate:
+            self.gate_at = sum(m.shape[0] for m in mats)
+            mats.append(tensors[self._name("gate")])
+            pad = -sum(m.shape[0] for m in mats) % 8       # rows of the packed output start on 16-byte boundaries
+            if pad:
+                mats.append(torch.zeros((pad, s.hidden_size), dtype=mats[0].dtype))
         wt = dtype if dtype == torch.bfloat16 else (torch.float32 if any(m.dtype == torch.float32 for m in mats) else torch.bfloat16)
         self.w_qkv = torch.cat([m.to(device=device, dtype=wt) for m in mats], dim=0).contiguous()
-        o = tensors[p + "o_proj.weight"]
+        o = tensors[self._name("o")]
         self.w_o = o.to(device=device, dtype=dtype if dtype == torch.bfloat16 else o.dtype).contiguous()
         if s.qk_norm_eps is not None:
-            self.q_norm = tensors[p + "q_norm.weight"].to(device=device, dtype=torch.float32).contiguous()
-            self.k_norm = tensors[p + "k_norm.weight"].to(device=device, dtype=torch.float32).contiguous()
+            self.q_norm = tensors[self._name("q_norm")].to(device=device, dtype=torch.float32).contiguous()
+            self.k_norm = tensors[self._name("k_norm")].to(device=device, dtype=torch.float32).contiguous()
         if self.position is not None:
             self.position.load(tensors, dtype, device)
 
@@ -76,14 +115,14 @@ class Attention(Mixer):
 
     def scratch_elements_per_token(self):
         s = self.spec
-        return (2 * s.num_heads + 2 * s.num_kv_heads) * s.head_dim + s.hidden_size
+        return (3 * s.num_heads + 2 * s.num_kv_heads) * s.head_dim + s.hidden_size + 8
 
     # ------------------------------------------------------------------ cache
     def cache_need(self):
         return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
     def takes_scaled_rows(self, num_rows):
-        return ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
+        return self.plain_form and ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
 
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_o)
@@ -101,10 +140,56 @@ class Attention(Mixer):
             ctx.memo[key] = angles
         return angles
 
+    # ------------------------------------------------- the general form, up to the output projection
+    def pre_output_width(self):
+        return self.spec.num_heads * self.spec.head_dim
+
+    def output_weight(self):
+        return self.w_o
+
+    def _attend(self, x, ctx, cache):
+        """Projection, preparation, cache store and attention of any form, kernel by kernel.  Returns the
+        heads' outputs [T, heads*head_dim] and the packed projection (whose gate columns the caller reads)."""
+        s = self.spec
+        T = x.shape[0]
+        nq, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        rot = self.position.rotary() if self.position is not None else None
+        inv_freq, rdim = rot if rot is not None else (None, 0)
+        eps = s.qk_norm_eps if s.qk_norm_eps is not None else 0.0
+        proj = ctx.ws.get("qkv", (T, self.w_qkv.shape[0]), x.dtype)
+        ops.gemm(x, self.w_qkv, proj)
+        kv = nkv if cache.writable else 0          # a run that reads another run's cache stores nothing
+        if self.plain_form:
+            ops.attention_prep(proj, ctx.positions, cache.slot_mapping if kv else None, self.q_norm, self.k_norm if kv else None,
+                               eps, inv_freq, rdim, cache.k if kv else None, cache.v if kv else None, nq, kv, hd,
+                               cache.page_size, angles=self._angles(proj, ctx, inv_freq, rdim) if kv else None)
+        else:
+            ops.attention_prep_row(proj, ctx.positions, cache.slot_mapping if kv else None, self.q_norm,
+                                   self.k_norm if kv else None, eps, inv_freq, rdim, self.pairing, s.values == "keys",
+                                   cache.k if kv else None, cache.v if kv else None, nq, kv, hd, cache.page_size)
+        attn = ctx.ws.get("attn_out", (T, nq * hd), x.dtype)
+        ops.paged_attention(proj[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token,
+                            cache.block_table, nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx)
+        return attn, proj
+
+    def forward_pre(self, x, ctx, cache, state, into, scale):
+        s = self.spec
+        attn, proj = self._attend(x, ctx, cache)
+        gate = proj[:, self.gate_at: self.gate_at + s.num_heads] if s.head_gate else None
+        ops.head_gate(attn, gate, scale, into, s.num_heads, s.head_dim)
+
     # ---------------------------------------------------------------- forward
     def forward(self, x, ctx, cache, state, sink=None):
         s = self.spec
         T = x.shape[0]
+        if not self.plain_form:
+            attn, proj = self._attend(x, ctx, cache)
+            if s.head_gate:
+                gated = ctx.ws.get("attn_gated", tuple(attn.shape), x.dtype)
+                ops.head_gate(attn, proj[:, self.gate_at: self.gate_at + s.num_heads], 1.0, gated, s.num_heads, s.head_dim)
+                attn = gated
+            out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
+            return None if ops.gemm(attn, self.w_o, out, sink=sink) else out
         nq, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
         rot = self.position.rotary() if self.position is not None else None
         inv_freq, rdim = rot if rot is not None else (None, 0)

@@ -37,7 +37,8 @@ class WeightDecl:
     """One checkpoint tensor a part binds by name.
 
     ``init`` tells the random-weights writer how to fill it: ``"normal"`` (zero
-    mean, the writer's sigma), ``"gain"`` (1 + U(-a, a)), ``"zeros"``."""
+    mean, the writer's sigma), ``"gain"`` (1 + U(-a, a)), ``"around_zero"`` (U(-a, a): a gain
+    stored minus one, a bias), ``"zeros"``."""
 
     name: str
     shape: Tuple[int, ...]
@@ -154,6 +155,21 @@ class Mixer(Part):
         another run's cache and must not store), ``state`` the state arena of this mixer
         ([slots, *shape]; rows ``ctx.state_slots`` belong to this step's
         requests) or None.  Returns the branch output [T, hidden]."""
+        raise NotImplementedError
+
+    # Optional: a mixer that can stop before its output projection, so that mixers standing side by side can
+    # share ONE output product over their concatenated inputs (``parts.parallel.ParallelMixer``).
+    def pre_output_width(self) -> Optional[int]:
+        """Width of what the output projection reads, or None when the mixer cannot stop before it."""
+        return None
+
+    def output_weight(self) -> torch.Tensor:
+        """The output projection [hidden, pre_output_width()]."""
+        raise NotImplementedError
+
+    def forward_pre(self, x: torch.Tensor, ctx, cache, state, into: torch.Tensor, scale: float) -> None:
+        """Everything up to the output projection; ``scale`` times its input goes into ``into``
+        [T, pre_output_width()] (columns of a wider buffer: unit inner stride, any row stride)."""
         raise NotImplementedError
 
 

@@ -1,12 +1,12 @@
-"""Gated feed-forward (SwiGLU): down(act(gate(x)) * up(x)), no biases
-(infer/src/model/qwen3/prefill.rs:291-337).  Gate and up are packed into one [2I, H]
+"""Gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is silu (SwiGLU,
+infer/src/model/qwen3/prefill.rs:291-337) or the tanh form of gelu.  Gate and up are packed into one [2I, H]
 matrix at load (cklxx/arle offers a packed layout as an option,
 infer/src/model/qwen3/weights.rs:98-122); here row 2i is gate_i and row 2i + 1 is up_i, so
 that the kernel that forms both sums of a pair can apply the gate itself."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import ClassVar
+from typing import ClassVar, Tuple
 
 import torch
 
@@ -20,26 +20,29 @@ class GatedMlpSpec:
     prefix: str
     hidden_size: int
     intermediate_size: int
-    activation: str = "silu"
+    activation: str = "silu"        # "silu" or "gelu_tanh"
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")   # after the prefix
     kind: ClassVar[str] = "gated_mlp"
 
 
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec):
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} not supported by the gated feed-forward (silu)")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} not supported by the gated feed-forward "
+                             f"({', '.join(ops.ACTIVATIONS)})")
         self.spec = spec
         self.w_gate_up = self.w_down = None
 
     def weight_decls(self):
         s, p = self.spec, self.spec.prefix
-        return (WeightDecl(p + "gate_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightDecl(p + "up_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightDecl(p + "down_proj.weight", (s.hidden_size, s.intermediate_size)))
+        g, u, d = s.names
+        return (WeightDecl(p + g, (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + u, (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + d, (s.hidden_size, s.intermediate_size)))
 
     def load(self, tensors, dtype, device):
         p = self.spec.prefix
-        g, u, d = (tensors[p + n + "_proj.weight"] for n in ("gate", "up", "down"))
+        g, u, d = (tensors[p + n] for n in self.spec.names)
         wt = dtype if dtype == torch.bfloat16 else (torch.float32 if torch.float32 in (g.dtype, u.dtype) else torch.bfloat16)
         g, u = g.to(device=device, dtype=wt), u.to(device=device, dtype=wt)
         self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
@@ -52,7 +55,8 @@ class GatedMlp(FeedForward):
         return 3 * self.spec.intermediate_size + self.spec.hidden_size
 
     def takes_scaled_rows(self, num_rows):
-        return ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
+        # the gate inside the weight-streaming product is silu
+        return self.spec.activation == "silu" and ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
 
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_down)
@@ -62,7 +66,7 @@ class GatedMlp(FeedForward):
         T = x.shape[0]
         gu = ctx.ws.get("gate_up", (T, 2 * s.intermediate_size), x.dtype)
         act = ctx.ws.get("ffn_act", (T, s.intermediate_size), x.dtype)
-        ops.gemm_silu_mul(x, self.w_gate_up, gu, act)
+        ops.gemm_act_mul(x, self.w_gate_up, gu, act, s.activation)
         out = ctx.ws.get("ffn_out", (T, s.hidden_size), x.dtype)
         if ops.gemm(act, self.w_down, out, sink=sink):
             return None                       # summed into the residual by the product itself

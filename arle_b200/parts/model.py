@@ -170,7 +170,7 @@ class DecoderModel:
         """The float32 residual [T, hidden] of this step's tokens."""
         resid = ctx.ws.get("residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
         ops.embedding(ctx.token_ids, self.embed, resid, None, getattr(ctx, "last_token", None),
-                      getattr(ctx, "slot_of_token", None))
+                      getattr(ctx, "slot_of_token", None), scale=self.spec.embed_scale)
         return resid
 
     def run_blocks(self, stream: ResidualStream, ctx) -> None:
@@ -186,6 +186,8 @@ class DecoderModel:
         final = stream.normed_rows(self.final_norm, ctx.want_rows, "final_normed")
         logits = ctx.ws.get("logits", (ctx.num_wanted, self.spec.vocab_size), torch.float32)
         ops.gemm(final, self.head, logits)
+        if self.spec.logit_cap:
+            ops.logit_cap(logits, self.spec.logit_cap)
         return logits
 
     def forward(self, ctx) -> Optional[torch.Tensor]:

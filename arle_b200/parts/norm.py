@@ -1,5 +1,7 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * weight, statistics in float32
-(crates/cuda-kernels/csrc/misc/norm.cu:221-300).  The gain is held in float32."""
+(crates/cuda-kernels/csrc/misc/norm.cu:221-300).  The gain is held in float32.
+With ``one_plus`` the checkpoint stores the gain around zero and the norm multiplies by
+1 + weight; the sum is formed once at load, in float32."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -17,6 +19,7 @@ class RmsNormSpec:
     weight_name: str
     size: int
     eps: float
+    one_plus: bool = False          # the stored weight is the gain minus one
     kind: ClassVar[str] = "rmsnorm"
 
 
@@ -27,10 +30,11 @@ class RmsNorm(Norm):
         self.weight = None
 
     def weight_decls(self):
-        return (WeightDecl(self.spec.weight_name, (self.spec.size,), init="gain"),)
+        return (WeightDecl(self.spec.weight_name, (self.spec.size,), init="around_zero" if self.spec.one_plus else "gain"),)
 
     def load(self, tensors, dtype, device):
-        self.weight = tensors[self.spec.weight_name].to(device=device, dtype=torch.float32).contiguous()
+        w = tensors[self.spec.weight_name].to(device=device, dtype=torch.float32)
+        self.weight = (w + 1.0 if self.spec.one_plus else w).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * 4

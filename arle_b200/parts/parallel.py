@@ -1,0 +1,150 @@
+"""Parts that stand side by side.
+
+``ParallelMixer``: several mixers read the same input and their outputs are added with fixed
+weights, y = sum_i scale_i * mixer_i(x).  When every member can stop before its output
+projection (``Mixer.pre_output_width``), each writes scale_i times that projection's input
+into its columns of one buffer and ONE product with the members' output matrices side by side
+gives y; otherwise every member runs whole and the outputs are summed by a kernel.  At most one
+member may keep a paged cache and at most one a state per request (the model hands a schedule
+entry one of each).
+
+``ParallelBlock``: x <- x + (mixer(n) + ff(n)) with n = norm(x): one norm, both branches read its
+output; the feed-forward may be absent.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar, Optional, Tuple
+
+import torch
+
+from .. import ops
+from .base import Block, Mixer
+from .registry import build_part, register_part
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    members: Tuple[object, ...]     # mixer specs
+    scales: Tuple[float, ...]       # one per member
+    hidden_size: int
+    kind: ClassVar[str] = "parallel_mixer"
+
+
+class ParallelMixer(Mixer):
+    def __init__(self, spec: ParallelMixerSpec):
+        if not spec.members or len(spec.members) != len(spec.scales):
+            raise ValueError("a parallel mixer needs members and one scale for each")
+        self.spec = spec
+        self.members = [build_part(m) for m in spec.members]
+        self.with_cache = [i for i, m in enumerate(self.members) if m.cache_need() is not None]
+        self.with_state = [i for i, m in enumerate(self.members) if m.state_need() is not None]
+        if len(self.with_cache) > 1 or len(self.with_state) > 1:
+            raise ValueError("a parallel mixer takes at most one member with a paged cache and one with a state")
+        widths = [m.pre_output_width() for m in self.members]
+        self.shared_output = all(w is not None for w in widths)
+        self.widths = widths if self.shared_output else None
+        self.w_o = None
+
+    def weight_decls(self):
+        return tuple(d for m in self.members for d in m.weight_decls())
+
+    def load(self, tensors, dtype, device):
+        for m in self.members:
+            m.load(tensors, dtype, device)
+        if self.shared_output:
+            # the members' output matrices side by side; columns padded so that every member's start on 16 bytes
+            mats, self.at, col = [], [], 0
+            for m, w in zip(self.members, self.widths):
+                wo = m.output_weight()
+                self.at.append(col)
+                mats.append(wo)
+                pad = -w % 8
+                if pad:
+                    mats.append(torch.zeros((wo.shape[0], pad), dtype=wo.dtype, device=wo.device))
+                col += w + pad
+            wt = torch.float32 if any(m_.dtype == torch.float32 for m_ in mats) else mats[0].dtype
+            self.w_o = torch.cat([m_.to(wt) for m_ in mats], dim=1).contiguous()
+            self.padded = any(-w % 8 for w in self.widths)
+
+    def weight_bytes(self):
+        return sum(m.weight_bytes() for m in self.members)
+
+    def scratch_elements_per_token(self):
+        return sum(m.scratch_elements_per_token() for m in self.members) + (self.w_o.shape[1] if self.w_o is not None else 0)
+
+    def cache_need(self):
+        return self.members[self.with_cache[0]].cache_need() if self.with_cache else None
+
+    def state_need(self):
+        return self.members[self.with_state[0]].state_need() if self.with_state else None
+
+    def can_sink(self, num_rows):
+        return self.shared_output and ops.fused_gemm_shape_ok(num_rows, self.w_o)
+
+    def _args(self, i, cache, state):
+        return (cache if i in self.with_cache else None, state if i in self.with_state else None)
+
+    def forward(self, x, ctx, cache, state, sink=None):
+        T = x.shape[0]
+        H = self.spec.hidden_size
+        if self.shared_output:
+            cat = ctx.ws.get("parallel_pre", (T, self.w_o.shape[1]), x.dtype)
+            if self.padded:
+                cat.zero_()
+            for i, (m, w) in enumerate(zip(self.members, self.widths)):
+                c, st = self._args(i, cache, state)
+                m.forward_pre(x, ctx, c, st, cat[:, self.at[i]: self.at[i] + w], self.spec.scales[i])
+            out = ctx.ws.get("mixer_out", (T, H), x.dtype)
+            return None if ops.gemm(cat, self.w_o, out, sink=sink) else out
+        total = None
+        for i, m in enumerate(self.members):
+            c, st = self._args(i, cache, state)
+            y = m.forward(x, ctx, c, st)
+            acc = ctx.ws.get(f"parallel_sum_{i & 1}", (T, H), x.dtype)
+            if total is None:
+                ops.weighted_sum(y, self.spec.scales[i], y, 0.0, acc)
+            else:
+                ops.weighted_sum(total, 1.0, y, self.spec.scales[i], acc)
+            total = acc
+        return total
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    norm: object
+    mixer: object
+    ffn: Optional[object]           # None: the block has no feed-forward
+    kind: ClassVar[str] = "parallel_block"
+
+
+class ParallelBlock(Block):
+    def __init__(self, spec: ParallelBlockSpec):
+        self.spec = spec
+        self.norm = build_part(spec.norm)
+        self.mixer = build_part(spec.mixer)
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self._parts = tuple(p for p in (self.norm, self.mixer, self.ffn) if p is not None)
+
+    def weight_decls(self):
+        return tuple(d for p in self._parts for d in p.weight_decls())
+
+    def load(self, tensors, dtype, device):
+        for p in self._parts:
+            p.load(tensors, dtype, device)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self._parts)
+
+    def scratch_elements_per_token(self):
+        return sum(p.scratch_elements_per_token() for p in self._parts)
+
+    def forward(self, stream, ctx, cache, state):
+        n = stream.normed(self.norm, "normed_a")
+        stream.add(self.mixer.forward(n, ctx, cache, state))
+        if self.ffn is not None:
+            stream.add(self.ffn.forward(n, ctx))
+
+
+register_part(ParallelMixerSpec.kind, ParallelMixer)
+register_part(ParallelBlockSpec.kind, ParallelBlock)

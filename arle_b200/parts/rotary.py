@@ -1,6 +1,8 @@
-"""Rotary position encoding, half-split pairing, over the first ``rotary_dim``
-elements of a head: inv_freq_i = theta^(-2i/rotary_dim), angle = position *
-inv_freq_i (infer/src/weight_loader.rs:955-989).  The reference tabulates cos and
+"""Rotary position encoding over the first ``rotary_dim`` elements of a head:
+inv_freq_i = theta^(-2i/rotary_dim), angle = position * inv_freq_i
+(infer/src/weight_loader.rs:955-989).  ``pairing`` says which two elements turn
+together: "half" pairs element i with i + rotary_dim/2 (Qwen3), "interleaved" pairs
+element 2i with 2i + 1.  The reference tabulates cos and
 sin of every position in bfloat16; here the kernels evaluate sincosf of the float32
 angle of the positions they meet (for prompt portions once per step, into a table
 that the step's layers share), so there is no limit on the position."""
@@ -19,6 +21,7 @@ from .registry import register_part
 class RotarySpec:
     rotary_dim: int
     theta: float
+    pairing: str = "half"
     kind: ClassVar[str] = "rotary"
 
 
@@ -26,6 +29,8 @@ class Rotary(PositionEncoding):
     def __init__(self, spec: RotarySpec):
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {spec.rotary_dim}")
+        if spec.pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing must be 'half' or 'interleaved', got {spec.pairing!r}")
         self.spec = spec
         self.inv_freq = None
 
@@ -36,6 +41,10 @@ class Rotary(PositionEncoding):
 
     def rotary(self):
         return self.inv_freq, self.spec.rotary_dim
+
+    @property
+    def pairing(self) -> str:
+        return self.spec.pairing
 
 
 register_part(RotarySpec.kind, Rotary)

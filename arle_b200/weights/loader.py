@@ -56,6 +56,13 @@ def _open_files(model_dir: str):
     raise FileNotFoundError(f"{model_dir}: neither model.safetensors nor model.safetensors.index.json")
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor of the checkpoint, from the files' headers alone.  For a configuration
+    class whose design leaves a size to a tensor's shape."""
+    files, _ = _open_files(model_dir)
+    return {n: tuple(f.info(n)[1]) for f in files.values() for n in f.names()}
+
+
 def kept_dtype(stored: torch.dtype, integer: bool) -> torch.dtype:
     if integer or not stored.is_floating_point:
         return torch.int32

@@ -90,14 +90,14 @@ def random_tensors(decls: Sequence[WeightDecl], seed: int, sigma: float = 0.02, 
             t = torch.zeros(d.shape, dtype=torch.int32, device=device)
         elif d.init == "zeros":
             t = torch.zeros(d.shape, dtype=dtype, device=device)
-        elif d.init in ("normal", "gain"):
+        elif d.init in ("normal", "gain", "around_zero"):
             flat = torch.empty(n, dtype=dtype, device=device)
             for at in range(0, n, _CHUNK):
                 m = min(_CHUNK, n - at)
                 if d.init == "normal":
                     v = _normal_chunk(key, at, m, sigma, device)
                 else:
-                    v = (_uniform_chunk(key, at, m, device) * 2.0 - 1.0) * float(gain_jitter) + 1.0
+                    v = (_uniform_chunk(key, at, m, device) * 2.0 - 1.0) * float(gain_jitter) + (1.0 if d.init == "gain" else 0.0)
                 flat[at:at + m] = v.to(dtype)
             t = flat.view(d.shape)
         else:

@@ -17,11 +17,11 @@ import torch
 F32 = torch.float32
 
 
-def embedding(ids, table, out, err=None, last_token=None, slot_of_token=None):
+def embedding(ids, table, out, err=None, last_token=None, slot_of_token=None, scale=1.0):
     ids = ids.long()
     if last_token is not None:
         ids = torch.where(ids < 0, last_token[slot_of_token.long()].long(), ids)
-    out.copy_(table[ids].to(F32))
+    out.copy_(table[ids].to(F32) * scale)
 
 
 def rmsnorm(resid, delta, rows, weight, eps, out, write_resid):
@@ -156,4 +156,98 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")
+ACTS = {"silu": lambda g: g / (1.0 + torch.exp(-g)),
+        "gelu_tanh": lambda g: 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))}
+
+
+def act_mul(gate_up, out, activation):
+    g, u = gate_up[:, 0::2].to(F32), gate_up[:, 1::2].to(F32)
+    out.copy_((ACTS[activation](g) * u).to(out.dtype))
+
+
+def gemm_act_mul(x, w, gate_up, out, activation="silu"):
+    gemm(x, w, gate_up)
+    act_mul(gate_up, out, activation)
+
+
+def attention_prep_row(qk, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys,
+                       k_cache, v_cache, nq, nkv, hd, page_size):
+    T = qk.shape[0]
+
+    def norm_rope(x, w, heads):
+        x = x.to(F32)
+        if w is not None:
+            x = x * (1.0 / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)) * w
+        x = x.view(T, heads, hd).clone()
+        if rotary_dim:
+            ang = positions.to(F32)[:, None] * inv_freq[None, :]
+            cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            if pairing == "half":
+                a, b = x[..., : rotary_dim // 2].clone(), x[..., rotary_dim // 2: rotary_dim].clone()
+                x[..., : rotary_dim // 2], x[..., rotary_dim // 2: rotary_dim] = a * cos - b * sin, b * cos + a * sin
+            else:
+                a, b = x[..., 0:rotary_dim:2].clone(), x[..., 1:rotary_dim:2].clone()
+                x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2] = a * cos - b * sin, b * cos + a * sin
+        return x
+
+    raw_k = qk[:, nq * hd:(nq + nkv) * hd].clone().view(T, nkv, hd) if nkv else None
+    q = norm_rope(qk[:, : nq * hd], q_weight, nq)
+    if nkv:
+        k = norm_rope(qk[:, nq * hd:(nq + nkv) * hd], k_weight, nkv).to(qk.dtype)
+        v = raw_k if values_are_keys else qk[:, (nq + nkv) * hd:(nq + 2 * nkv) * hd].view(T, nkv, hd)
+        keep = slot_mapping >= 0
+        page = (slot_mapping[keep] // page_size).long()
+        off = (slot_mapping[keep] % page_size).long()
+        k_cache[page, :, off] = k[keep]
+        v_cache[page, :, off] = v[keep]
+    qk[:, : nq * hd] = q.reshape(T, nq * hd).to(qk.dtype)
+
+
+def head_gate(x, gate, scale, out, heads, hd):
+    T = x.shape[0]
+    y = x.to(F32).view(T, heads, hd)
+    if gate is not None:
+        y = y * (1.0 / (1.0 + torch.exp(-gate.to(F32))))[:, :, None]
+    out.copy_((y * scale).reshape(T, heads * hd).to(out.dtype))
+
+
+def weighted_sum(x, a, y, b, out):
+    out.copy_((a * x.to(F32) + b * y.to(F32)).to(out.dtype))
+
+
+def logit_cap(logits, cap):
+    logits.copy_(cap * torch.tanh(logits / cap))
+
+
+def gla_decay(low, w2, bias, tau, alpha):
+    z = low.to(F32) @ w2.t()
+    if bias is not None:
+        z = z + bias
+    alpha.copy_(torch.exp(-torch.nn.functional.softplus(-z) / tau))
+
+
+def gla_scan(q, k, v, alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale, max_q_len):
+    for r in range(state_slots.numel()):
+        S = state[int(state_slots[r])]                                   # [heads, vdim, dim]
+        for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+            qt = q[t].to(F32).view(heads, dim) * q_scale
+            kt, vt, at = k[t].to(F32).view(heads, dim), v[t].to(F32).view(heads, vdim), alpha[t].view(heads, dim)
+            S.copy_(S * at[:, None, :] + vt[:, :, None] * kt[:, None, :])
+            out[t] = torch.einsum("hvd,hd->hv", S, qt).reshape(-1)
+
+
+def gla_out(o, gate, weight, eps, scale, out, heads, vdim):
+    T = o.shape[0]
+    y = o.view(T, heads, vdim)
+    y = y * (1.0 / torch.sqrt((y * y).mean(dim=-1, keepdim=True) + eps))
+    if weight is not None:
+        y = y * weight
+    y = y.reshape(T, heads * vdim)
+    if gate is not None:
+        g = gate.to(F32)
+        y = y * (g / (1.0 + torch.exp(-g)))
+    out.copy_((y * scale).to(out.dtype))
+
+
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample",
+       "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out")
