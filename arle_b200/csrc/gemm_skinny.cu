@@ -358,11 +358,14 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) s += rb[(size_t)w * 16 * NT * 8];
       if (gated) {
-        // rows 2i and 2i+1 of W are gate_i and up_i: out[m, i] = silu(gate) * up, in float32
+        // rows 2i and 2i+1 of W are gate_i and up_i: out[m, i] = act(gate) * up, in float32 (gated 1: silu;
+        // 2: the tanh form of gelu)
         s *= row_scale[m];
         const float up = __shfl_down_sync(0xffffffffu, s, 1);
         if (!(row & 1) && m < M && rt + row < r1)
-          store_out<OutT>(out + (size_t)m * ldo + ((rt + row) >> 1), s / (1.0f + expf(-s)) * up);
+          store_out<OutT>(out + (size_t)m * ldo + ((rt + row) >> 1),
+                          (gated == 2 ? 0.5f * s * (1.0f + tanhf(0.7978845608028654f * (s + 0.044715f * s * s * s)))
+                                      : s / (1.0f + expf(-s))) * up);
       } else if (csize == 1) {
         ss_acc += finish(s * row_scale[m], m, rt + row, m < M && rt + row < r1, sink_r, sink_g);
       } else {
@@ -554,6 +557,7 @@ ARLE_API int arle_gemm_skinny_gated(const void* x, int ldx, const void* W, int l
 // The same two products with the fusions described at the top of the file.
 //  in_ss (may be null): float32 [16][192], sums of squares of x's rows as left by an earlier launch
 //    with a sink; the sums of this product are multiplied by rsqrt(sum(in_ss[m, :]) * inv_width + eps).
+//  gated: 0 plain product; 1 the gate is silu; 2 the gate is the tanh form of gelu.
 //  resid (may be null; not with gated): float32 [M, ldr].  When given, nothing goes to out (it may be
 //    null): resid[m, n] += sum, xs[m, n] = bfloat16(resid[m, n] * gamma[n]), and out_ss [16][192] gets
 //    the sums of squares of the new residual rows, every slot written.

@@ -92,7 +92,7 @@ template <int STAGES, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                         const __grid_constant__ CUtensorMap map_w,
                                                                         OutT* __restrict__ out, int ldo, int M, int N,
-                                                                        int K, int* __restrict__ err) {
+                                                                        int K, int act, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE = A_BYTES + B_BYTES;
@@ -228,7 +228,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_pair_kernel(const __
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
-            v[i] = g / (1.0f + __expf(-g)) * u;
+            v[i] = (act == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                             : g / (1.0f + __expf(-g))) * u;
           }
           if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
             uint32_t p[8];
@@ -295,7 +296,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_pair_kernel(const __
 }
 
 template <int STAGES, bool GATED, typename OutT>
-int launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int* err, cudaStream_t s) {
+int launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int act, int* err,
+           cudaStream_t s) {
   CUtensorMap mx, mw;
   int rc = tensor_map_2d_bf16(x, M, K, ldx, BM, &mx);
   if (rc) return rc;
@@ -315,7 +317,7 @@ int launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, i
   const long long num_tiles = (long long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
   long long pairs = sms / 2;
   if (num_tiles < pairs) pairs = num_tiles;
-  cudaError_t e = launch_kernel(kern, dim3((unsigned)(2 * pairs)), dim3(kThreads), smem, s, 2, mx, mw, (OutT*)out, ldo, M, N, K, err);
+  cudaError_t e = launch_kernel(kern, dim3((unsigned)(2 * pairs)), dim3(kThreads), smem, s, 2, mx, mw, (OutT*)out, ldo, M, N, K, act, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
@@ -323,7 +325,7 @@ int launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, i
 }  // namespace
 
 // out_dtype: 0 float32, 1 bfloat16.  gated != 0: W holds (gate_i, up_i) in rows 2i and 2i + 1 and out is bfloat16
-// [M, N / 2] (N even).  Needs K, ldx, ldw multiples of 8 and 16-byte aligned x and W.  err: set to 3 if a bounded
+// [M, N / 2] (N even); gated 1: the gate is silu, 2: the tanh form of gelu.  Needs K, ldx, ldw multiples of 8 and 16-byte aligned x and W.  err: set to 3 if a bounded
 // wait ran out.
 ARLE_API int arle_gemm_tcgen05_pair(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
                                     int N, int K, int gated, int* err, cudaStream_t s) {
@@ -332,9 +334,9 @@ ARLE_API int arle_gemm_tcgen05_pair(const void* x, int ldx, const void* W, int l
   if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
   if (gated) {
     if (N % 2 != 0 || out_dtype != 1) return ARLE_E_BADARG;
-    return launch<6, true, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
+    return launch<6, true, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
   }
-  if (out_dtype == 1) return launch<6, false, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-  if (out_dtype == 0) return launch<6, false, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
+  if (out_dtype == 1) return launch<6, false, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, 0, err, s);
+  if (out_dtype == 0) return launch<6, false, float>(x, ldx, W, ldw, out, ldo, M, N, K, 0, err, s);
   return ARLE_E_BADARG;
 }

@@ -419,10 +419,11 @@ def gemm_tcgen05(x, w, out) -> None:
                                        K, _ptr(error_flag(x.device)), _stream()), "gemm_tcgen05")
 
 
-def gemm_tcgen05_pair(x, w, out, gated: bool = False) -> None:
+def gemm_tcgen05_pair(x, w, out, gated: bool = False, activation: str = "silu") -> None:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores with two SMs to a 256 x 256 tile
     (``cta_group::2``).  ``gated``: w holds (gate_i, up_i) in rows 2i and 2i + 1 and out [M, N / 2] gets
-    silu(gate) * up, the gate applied to the float32 sums in the kernel's epilogue."""
+    act(gate) * up (``activation`` "silu" or "gelu_tanh"), the gate applied to the float32 sums in the kernel's
+    epilogue."""
     M, K = x.shape
     N = w.shape[0]
     No = N // 2 if gated else N
@@ -430,8 +431,8 @@ def gemm_tcgen05_pair(x, w, out, gated: bool = False) -> None:
             or (gated and (N % 2 or out.dtype != torch.bfloat16))):
         raise KernelError(f"gemm_tcgen05_pair: unsupported operands x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     _check(library().arle_gemm_tcgen05_pair(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0), M,
-                                            N, K, int(bool(gated)), _ptr(error_flag(x.device)), _stream()),
-           "gemm_tcgen05_pair")
+                                            N, K, (1 + ACTIVATIONS[activation]) if gated else 0, _ptr(error_flag(x.device)),
+                                            _stream()), "gemm_tcgen05_pair")
 
 
 def skinny_gemm_supported(x, w, out) -> bool:
@@ -782,11 +783,23 @@ def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
 
 
 def gemm_act_mul(x, w: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
-    """The first half of a gated feed-forward with the named activation on the gate.  "silu" takes the fused
-    kernels of ``gemm_silu_mul`` where the shapes allow them; other activations run the product and then the
-    gate kernel."""
+    """The first half of a gated feed-forward with the named activation on the gate: ``gemm_silu_mul`` for any
+    of ``ACTIVATIONS`` (the same fused kernels where the shapes allow them, else the product and the gate kernel)."""
     if activation == "silu":
         gemm_silu_mul(x, w, gate_up, out)
+        return
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_act_mul: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    T, I = out.shape
+    if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I):
+        raise KernelError(f"gemm_act_mul: shapes w {tuple(w.shape)} gate_up {tuple(gate_up.shape)} out {tuple(out.shape)}")
+    if (_KERNEL_SET == "fast" and not isinstance(x, ScaledRows) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and fused_gemm_supported(x, w) and skinny_gemm_supported(x, w, out) and gated_gemm_fits(x.shape[1])):
+        _fused_gemm(x, w, out, 1 + ACTIVATIONS[activation], None, None)
+        return
+    if (_KERNEL_SET == "fast" and T >= _GATED_TCGEN05_MIN_ROWS and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and tcgen05_gemm_supported(x, w, out)):
+        gemm_tcgen05_pair(x, w, out, gated=True, activation=activation)
         return
     gemm(x, w, gate_up)
     act_mul(gate_up, out, activation)

@@ -14,6 +14,9 @@ through ``Engine.generate`` with token ids going in from and coming back to the
 host.  Weights are seeded random, token ids uniform random, the cache of the
 device-timed runs is filled with random values (synthetic data).  The engine is a
 single-GPU one: for --gpus above 1 it says so and exits with 2.
+
+``--design kolodra`` leaves the default workload alone and prints another record: a few Kolodra layers
+beside as many Qwen3 layers of equal sizes, prefill and decode, with every kernel's time per layer.
 """
 import argparse
 import json
@@ -146,6 +149,122 @@ def gemm_table(args, sizes, torch, ops) -> int:
     return 0
 
 
+# Layer sizes for ``--design kolodra``: the softmax side, the width and the feed-forward of a Kolodra layer equal a
+# Qwen3 layer's (0.6B and 8B sizes); the recurrent side comes on top (half as many heads, 128 x 128 states).
+DESIGN_SIZES = {"0.6b": dict(width=1024, ff=3072, heads=16, kv=8, hd=128, rheads=8, rank=16, vocab=32768),
+                "8b": dict(width=4096, ff=12288, heads=32, kv=8, hd=128, rheads=16, rank=64, vocab=32768)}
+
+
+def design_table(args, torch, ops, pk) -> int:
+    """``--design kolodra``: prefill and decode throughput of a few Kolodra layers beside the same number of Qwen3
+    layers of equal width, heads and feed-forward, with the device time of every kernel of one step (profiler
+    timeline of a step, summed by kernel name and divided by the layers).  One JSON line."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from arle_b200.engine import ModelRunner, StepEntry, random_model
+
+    dev = torch.device("cuda:0")
+    L, T, C = args.layers or 4, args.prefill_tokens, args.context
+    gen = torch.Generator().manual_seed(1)
+    out = {"design": "kolodra", "layers": L, "prefill_tokens": T, "context": C, "dtype": "bf16", "peaks": pk, "sizes": {}}
+
+    def kolodra_config(z):
+        layer = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["ff"]},
+                 "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
+                                    "rot": {"base": 1e6, "dims": z["hd"]}},
+                           "right": {"heads": z["rheads"], "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": z["rank"]},
+                           "left_scale": 1.0, "right_scale": 1.0}}
+        return {"architecture": "Kolodra", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+                "logit_softcap": 30.0, "layers": [layer] * L}
+
+    def qwen_config(z):
+        return dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv"],
+                    head_dim=z["hd"], intermediate_size=z["ff"], vocab_size=z["vocab"])
+
+    def timeline(fn):
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        by = {}
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0][:48]
+                by[name] = by.get(name, 0.0) + (e.time_range.end - e.time_range.start)
+        return {k: round(v / L, 2) for k, v in sorted(by.items(), key=lambda kv: -kv[1])}
+
+    def measure(cfg):
+        model = random_model(cfg, seed=0, dtype="bfloat16", device=dev)
+        vocab = model.spec.vocab_size
+        res = {"weight_bytes_per_step": int(model.weight_bytes_per_step())}
+        batches = (8, 64)
+        per_req = C + args.steps + args.warmup + 80
+        runner = ModelRunner(model, 16, max(batches) * -(-per_req // 16) + -(-T // 16) + 64, max(batches) + 1, max(per_req, T) + 64, dev)
+        if not args.no_cuda_graph:
+            runner.enable_graphs()
+        for g in runner.cache.groups:
+            for a in g.arrays:
+                a.normal_(0.0, 0.5)
+        res["cache_bytes_per_token"] = int(runner.cache.bytes_per_token())
+        res["state_bytes_per_request"] = int(sum(s[0].numel() * s.element_size() for s in runner.cache.states))
+
+        def prefill(tag):
+            ids = torch.randint(0, vocab, (T,), generator=gen).tolist()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            runner.step([StepEntry(tag, ids, (T - 1,))])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.end_request(tag)
+            return e0.elapsed_time(e1)
+
+        for i in range(3):
+            prefill(f"w{i}")
+        ms = sorted(prefill(f"t{i}") for i in range(5))[2]
+        res["prefill"] = {"ms": round(ms, 3), "ms_per_layer": round(ms / L, 4), "tokens_per_s": round(T * 1000.0 / ms, 1),
+                          "kernels_us_per_layer": timeline(lambda: prefill("prof"))}
+        for b in batches:
+            rids = [f"d{b}-{i}" for i in range(b)]
+            for r in rids:
+                runner.add_request(r)
+            runner.cache.append([(r, C - 1) for r in rids])
+            for st in runner.cache.states:
+                st.normal_(0.0, 0.1)
+
+            def one():
+                toks = torch.randint(0, vocab, (b,), generator=gen).tolist()
+                runner.step([StepEntry(r, [t], (0,)) for r, t in zip(rids, toks)])
+
+            for _ in range(args.warmup):
+                one()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = ops.launch_count()
+            e0.record()
+            for _ in range(args.steps):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "ms_per_layer": round(ms / L, 4), "tokens_per_s": round(b * 1000.0 / ms, 1),
+                                   "launches_per_step": (ops.launch_count() - l0) // args.steps,
+                                   "kernels_us_per_layer": timeline(one)}
+            for r in rids:
+                runner.end_request(r)
+        ops.check_errors(dev)
+        del runner, model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        return res
+
+    for name in ([args.sizes] if args.sizes in DESIGN_SIZES and args.sizes != "8b" else list(DESIGN_SIZES)):
+        z = DESIGN_SIZES[name]
+        out["sizes"][name] = {"config": z, "kolodra": measure(kolodra_config(z)), "qwen3": measure(qwen_config(z))}
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -166,6 +285,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: tokens each request holds")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: tokens of the prompt")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--design", default=None, choices=["kolodra"],
+                    help="instead of the default workload: a few layers of this design beside as many Qwen3 layers of equal "
+                         "sizes, prefill and decode, with every kernel's time (uses --layers, --steps, --context, --prefill-tokens)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: also the kernels of one graph-replayed step in order, with the device time "
                          "of each (from torch's profiler: shares of the step, not a benchmark figure)")
@@ -183,7 +305,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
-    if args.only == "all" and (args.context != CONTEXT or args.prefill_tokens != PREFILL_TOKENS):
+    if args.only == "all" and not args.design and (args.context != CONTEXT or args.prefill_tokens != PREFILL_TOKENS):
         print("bench.py: --context and --prefill-tokens go with --only decode / --only prefill; the full run keeps the contract's sizes")
         return 2
     globals()["CONTEXT"], globals()["PREFILL_TOKENS"] = args.context, args.prefill_tokens
@@ -205,6 +327,8 @@ def main() -> int:
         ops.set_gated_tcgen05_min_rows(args.gated_min_rows)
     pk = peaks()
     sizes = SIZES[args.sizes]
+    if args.design:
+        return design_table(args, torch, ops, pk)
     if args.only == "gemm":
         return gemm_table(args, sizes, torch, ops)
     layers = args.layers or sizes["num_hidden_layers"]

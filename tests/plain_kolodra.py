@@ -22,6 +22,28 @@ import torch
 
 DT = torch.float64
 
+# What a 16-bit engine keeps between kernels can be imitated: ``with stored_as(torch.bfloat16):`` rounds every
+# activation that such an engine writes to memory (projections, normed rows, heads' outputs, branch outputs), while the
+# arithmetic in between stays float64.  The distance between such a run and the exact one is what rounding alone
+# costs on a given model and prompt; the tests allow the engine a small multiple of it.
+_STORE = [None]
+
+
+class stored_as:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        _STORE.append(self.dtype)
+
+    def __exit__(self, *exc):
+        _STORE.pop()
+        return False
+
+
+def st(x):
+    return x if _STORE[-1] is None else x.to(_STORE[-1]).to(DT)
+
 
 # ------------------------------------------------------------------- elementary
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -70,14 +92,14 @@ def softmax_side(n, w, p: str, m: dict, eps: float, start: int = 0):
     T = n.shape[0]
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     pos = torch.arange(start, start + T)
-    q = n @ w[p + "q"].T
-    k = n @ w[p + "k"].T
+    q = st(n @ w[p + "q"].T)
+    k = st(n @ w[p + "k"].T)
     v = k.reshape(T, G, d)
     q = (rms(q, eps) * w[p + "q.norm"]).reshape(T, H, d)
     k = (rms(k, eps) * w[p + "k.norm"]).reshape(T, G, d)
-    q = rotate_interleaved(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_interleaved(k, pos, m["rot"]["base"], m["rot"]["dims"])
-    gate = sigmoid(n @ w[p + "g"].T)                                               # [T, H]
+    q = st(rotate_interleaved(q, pos, m["rot"]["base"], m["rot"]["dims"]))
+    k = st(rotate_interleaved(k, pos, m["rot"]["base"], m["rot"]["dims"]))
+    gate = sigmoid(st(n @ w[p + "g"].T))                                           # [T, H]
     out = torch.zeros(T, H, d, dtype=n.dtype)
     mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
     for h in range(H):
@@ -85,14 +107,14 @@ def softmax_side(n, w, p: str, m: dict, eps: float, start: int = 0):
         sc = (q[:, h] @ k[:, g].T) * m["scale"]
         sc = sc.masked_fill(~mask, float("-inf"))
         out[:, h] = torch.softmax(sc, dim=-1) @ v[:, g]
-    out = out * gate[:, :, None]
-    return out.reshape(T, H * d) @ w[p + "o"].T
+    out = st(st(out) * gate[:, :, None])
+    return st(out.reshape(T, H * d) @ w[p + "o"].T)
 
 
 # ---------------------------------------------------------------- recurrent side
 def decay(n, w, p: str, m: dict):
     """alpha [T, heads, dim] = sigmoid(W_a2 (W_a1 n) + b)^(1/tau)."""
-    z = (n @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "a2.b"]
+    z = st(n @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "a2.b"]
     return (sigmoid(z) ** (1.0 / m["tau"])).reshape(n.shape[0], m["heads"], m["dim"])
 
 
@@ -102,9 +124,9 @@ def recurrent_side(n, w, p: str, m: dict, eps: float, state=None):
     the heads), multiplied by silu(W_g n) and projected."""
     T = n.shape[0]
     H, d, dv = m["heads"], m["dim"], m["vdim"]
-    q = (n @ w[p + "q"].T).reshape(T, H, d) * d ** -0.5
-    k = (n @ w[p + "k"].T).reshape(T, H, d)
-    v = (n @ w[p + "v"].T).reshape(T, H, dv)
+    q = st(n @ w[p + "q"].T).reshape(T, H, d) * d ** -0.5
+    k = st(n @ w[p + "k"].T).reshape(T, H, d)
+    v = st(n @ w[p + "v"].T).reshape(T, H, dv)
     a = decay(n, w, p, m)
     S = torch.zeros(H, d, dv, dtype=n.dtype) if state is None else state
     o = torch.zeros(T, H, dv, dtype=n.dtype)
@@ -112,19 +134,19 @@ def recurrent_side(n, w, p: str, m: dict, eps: float, state=None):
         S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hdv,hd->hv", S, q[t])
     o = rms(o, eps) * w[p + "norm"]
-    o = o.reshape(T, H * dv) * silu(n @ w[p + "g"].T)
-    return o @ w[p + "o"].T, S
+    o = st(o.reshape(T, H * dv) * silu(st(n @ w[p + "g"].T)))
+    return st(o @ w[p + "o"].T), S
 
 
 def parallel_mixer(n, w, p: str, m: dict, eps: float):
     left = softmax_side(n, w, p + "left.", m["left"], eps)
     right, _ = recurrent_side(n, w, p + "right.", m["right"], eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return st(m["left_scale"] * left + m["right_scale"] * right)
 
 
 # ------------------------------------------------------------------ feed-forward
 def dense_ff(n, w, p: str):
-    return (gelu_tanh(n @ w[p + "gate"].T) * (n @ w[p + "up"].T)) @ w[p + "down"].T
+    return st(st(gelu_tanh(st(n @ w[p + "gate"].T)) * st(n @ w[p + "up"].T)) @ w[p + "down"].T)
 
 
 # ------------------------------------------------------------------------ model
@@ -138,7 +160,7 @@ def layer(x, w, cfg: dict, i: int):
     if e["type"] != "parallel":
         raise ValueError(f"layer type {e['type']!r}")
     p, eps = layer_prefix(cfg, i), cfg["norm"]["eps"]
-    n = norm_one_plus(x, w[p + "norm1"], eps)
+    n = st(norm_one_plus(x, w[p + "norm1"], eps))
     y = parallel_mixer(n, w, p + "mix.", e["mixer"], eps)
     if e.get("mlp") is not None:
         if e["mlp"]["kind"] != "dense":
@@ -155,7 +177,7 @@ def forward(w: dict, cfg: dict, tokens, trace: list = None) -> torch.Tensor:
         x = layer(x, w, cfg, i)
         if trace is not None:
             trace.append(x)
-    y = norm_one_plus(x, w["final.norm"], cfg["norm"]["eps"]) @ w["head"].T
+    y = st(norm_one_plus(x, w["final.norm"], cfg["norm"]["eps"])) @ w["head"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(y / cap) if cap else y
 
