@@ -7,7 +7,7 @@
 //
 //  * gla_decay: alpha[t, c] = sigmoid(z)^(1/tau), z = b[c] + sum_r low[t, r] * w2[c, r], the second
 //    half of a low-rank gate (low = W_a1 x comes from the packed input projection).  Evaluated as
-//    exp(-softplus(-z) / tau) in float32.
+//    exp(-softplus(-z) / tau) in float32; a block takes eight tokens and 256 channels, r ascending.
 //  * gla_scan: the recurrence over this step's tokens of every request row, from the state that the
 //    request's slot holds, which is left updated.  Float32 throughout; q, k, v are read in the
 //    activation type.  One block per (columns of vdim, head, row); a thread keeps 16 consecutive key
@@ -23,56 +23,83 @@ using namespace arle;
 
 constexpr int kScanThreads = 128;
 constexpr int kScanDpt = 16;                     // key channels per thread
+constexpr int kScanPad = 20;                     // floats a thread's 16 channels take in shared memory (16-byte rows, spread over the banks)
+constexpr int kDecayTokens = 8;                  // tokens a block of the decay kernel takes
 
+// w2t is the second matrix of the gate transposed, [rank][channels]: consecutive threads read consecutive floats.
 template <typename T>
-__global__ void gla_decay_kernel(const T* __restrict__ low, int low_stride, const float* __restrict__ w2,
-                                 const float* __restrict__ bias, float inv_tau, float* __restrict__ alpha, int channels,
-                                 int rank) {
+__global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ low, int low_stride, const float* __restrict__ w2t,
+                                                        const float* __restrict__ bias, float inv_tau, float* __restrict__ alpha,
+                                                        int num_tokens, int channels, int rank) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float lo_s[];                // rank floats
-  const int t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) lo_s[r] = to_f32(low[(size_t)t * low_stride + r]);
+  extern __shared__ float lo_s[];                // [kDecayTokens][rank]
+  const int t0 = blockIdx.x * kDecayTokens;
+  const int n = min(kDecayTokens, num_tokens - t0);
+  for (int i = threadIdx.x; i < kDecayTokens * rank; i += blockDim.x) {
+    const int tt = i / rank, r = i - tt * rank;
+    lo_s[i] = tt < n ? to_f32(low[(size_t)(t0 + tt) * low_stride + r]) : 0.f;
+  }
   __syncthreads();
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-    const float* wr = w2 + (size_t)c * rank;
-    float z = 0.f;
-    for (int r = 0; r < rank; ++r) z = fmaf(lo_s[r], wr[r], z);
-    if (bias) z += bias[c];
-    const float y = -z;                          // softplus(y) = log(1 + e^y), the stable way
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  float z[kDecayTokens];
+#pragma unroll
+  for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = 0.f;
+  for (int r = 0; r < rank; ++r) {
+    const float w = w2t[(size_t)r * channels + c];
+#pragma unroll
+    for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(lo_s[tt * rank + r], w, z[tt]);
+  }
+  const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+  for (int tt = 0; tt < kDecayTokens; ++tt) {
+    if (tt >= n) break;
+    const float y = -(z[tt] + b);                // softplus(y) = log(1 + e^y), the stable way
     const float sp = y > 0.f ? y + log1pf(expf(-y)) : log1pf(expf(y));
-    alpha[(size_t)t * channels + c] = expf(-sp * inv_tau);
+    alpha[(size_t)(t0 + tt) * channels + c] = expf(-sp * inv_tau);
   }
 }
 
-template <typename T>
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+// LPC: lanes that share a column of the state (a power of two; LPC * 16 >= dim).  VEC: four channels at a time can be
+// fetched with one aligned load.  A chunk of CHUNK tokens is staged in shared memory; while it is worked on, the next
+// chunk's q, k, alpha and v are already on their way into registers.
+template <typename T, int LPC, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
     const float* __restrict__ alpha, float* __restrict__ state, const int* __restrict__ q_indptr,
-    const int* __restrict__ state_slots, float* __restrict__ out, int heads, int dim, int vdim, int lpc, int chunk,
-    float q_scale) {
+    const int* __restrict__ state_slots, float* __restrict__ out, int heads, int dim, int vdim, float q_scale) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
-  const int cols = kScanThreads / lpc;
-  const int dpad = (kScanDpt + 1) * lpc;         // channel c sits at c + c / 16: lanes of a column hit different banks
-  float* qs = sm;                                // [chunk][dpad]
-  float* ks = qs + (size_t)chunk * dpad;
-  float* as = ks + (size_t)chunk * dpad;
-  float* vs = as + (size_t)chunk * dpad;         // [chunk][cols]
-  const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * cols;
-  const int l = threadIdx.x & (lpc - 1), jl = threadIdx.x / lpc;
+  constexpr int COLS = kScanThreads / LPC;
+  constexpr int DSPAN = kScanDpt * LPC;          // dim rounded up; channels past dim hold zeros
+  constexpr int DPAD = kScanPad * LPC;
+  constexpr int CHUNK = LPC >= 8 ? 128 / LPC : 16;               // 16 tokens (8 and 4 for the widest heads)
+  constexpr int QUADS = CHUNK * DSPAN / 4;                       // groups of four channels in a chunk
+  constexpr int QPT = (QUADS + kScanThreads - 1) / kScanThreads;             // per thread: at most four
+  constexpr int VPT = (CHUNK * COLS + kScanThreads - 1) / kScanThreads;      // values per thread
+  __shared__ __align__(16) float qs[CHUNK * DPAD], ks[CHUNK * DPAD], as[CHUNK * DPAD];
+  __shared__ float vs[CHUNK * COLS];
+  const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * COLS;
+  const int l = threadIdx.x & (LPC - 1), jl = threadIdx.x / LPC;
   const int j = j0 + jl;
   const bool col_ok = j < vdim;
   const int t_begin = q_indptr[r], t_end = q_indptr[r + 1];
   // the state of a head is kept as [vdim][dim]: a thread's 16 channels of its column are contiguous
   float* S_g = state + (((size_t)state_slots[r] * heads + h) * vdim + (col_ok ? j : 0)) * dim + l * kScanDpt;
-  const bool vec = (dim & 3) == 0;
+  const bool vec_state = (dim & 3) == 0;
   float S[kScanDpt];
 #pragma unroll
   for (int i = 0; i < kScanDpt; i += 4) {
     const int c = l * kScanDpt + i;
-    if (vec) {
+    if (vec_state) {
       float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
       if (col_ok && c < dim) u = *reinterpret_cast<const float4*>(S_g + i);
       S[i] = u.x, S[i + 1] = u.y, S[i + 2] = u.z, S[i + 3] = u.w;
@@ -82,44 +109,94 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     }
   }
   const size_t hq = (size_t)h * dim, hv = (size_t)h * vdim;
-  const int dspan = kScanDpt * lpc;              // dim rounded up; channels past dim hold zeros
-  for (int t0 = t_begin; t0 < t_end; t0 += chunk) {
-    const int n = min(chunk, t_end - t0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < n * dspan; idx += kScanThreads) {
-      const int tt = idx / dspan, c = idx - tt * dspan;
-      const size_t row = (size_t)(t0 + tt);
-      const bool ok = c < dim;
-      const int at = tt * dpad + c + c / kScanDpt;
-      qs[at] = ok ? to_f32(q[row * in_stride + hq + c]) * q_scale : 0.f;
-      ks[at] = ok ? to_f32(k[row * in_stride + hq + c]) : 0.f;
-      as[at] = ok ? alpha[row * heads * dim + hq + c] : 0.f;
+  const size_t a_stride = (size_t)heads * dim;
+  float4 rq[QPT], rk[QPT], ra[QPT];
+  float rv[VPT];
+
+  auto fetch = [&](int t0, int n) {              // the chunk's numbers into registers; nothing waits on them yet
+#pragma unroll
+    for (int u = 0; u < QPT; ++u) {
+      const int idx = threadIdx.x + u * kScanThreads;
+      const int tt = idx / (DSPAN / 4), c = (idx - tt * (DSPAN / 4)) * 4;
+      float4 fq = make_float4(0.f, 0.f, 0.f, 0.f), fk = fq, fa = fq;
+      if (idx < QUADS && tt < n && c < dim) {
+        const size_t row = (size_t)(t0 + tt);
+        if (VEC) {
+          fq = load4(q + row * in_stride + hq + c);
+          fk = load4(k + row * in_stride + hq + c);
+          fa = load4(alpha + row * a_stride + hq + c);
+        } else {
+          float* pq = &fq.x; float* pk = &fk.x; float* pa = &fa.x;
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (c + e < dim) {
+              pq[e] = to_f32(q[row * in_stride + hq + c + e]);
+              pk[e] = to_f32(k[row * in_stride + hq + c + e]);
+              pa[e] = alpha[row * a_stride + hq + c + e];
+            }
+        }
+      }
+      rq[u] = fq, rk[u] = fk, ra[u] = fa;
     }
-    for (int idx = threadIdx.x; idx < n * cols; idx += kScanThreads) {
-      const int tt = idx / cols, c = idx - tt * cols;
-      vs[idx] = j0 + c < vdim ? to_f32(v[(size_t)(t0 + tt) * in_stride + hv + j0 + c]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int idx = threadIdx.x + u * kScanThreads;
+      const int tt = idx / COLS, c = idx - tt * COLS;
+      rv[u] = (idx < CHUNK * COLS && tt < n && j0 + c < vdim) ? to_f32(v[(size_t)(t0 + tt) * in_stride + hv + j0 + c]) : 0.f;
     }
+  };
+  auto stage = [&]() {                           // registers to shared memory, q scaled on the way
+#pragma unroll
+    for (int u = 0; u < QPT; ++u) {
+      const int idx = threadIdx.x + u * kScanThreads;
+      const int tt = idx / (DSPAN / 4), c = (idx - tt * (DSPAN / 4)) * 4;
+      const int at = tt * DPAD + (c / kScanDpt) * kScanPad + (c % kScanDpt);
+      if (idx >= QUADS) continue;
+      *reinterpret_cast<float4*>(qs + at) = make_float4(rq[u].x * q_scale, rq[u].y * q_scale, rq[u].z * q_scale, rq[u].w * q_scale);
+      *reinterpret_cast<float4*>(ks + at) = rk[u];
+      *reinterpret_cast<float4*>(as + at) = ra[u];
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u)
+      if (threadIdx.x + u * kScanThreads < CHUNK * COLS) vs[threadIdx.x + u * kScanThreads] = rv[u];
+  };
+
+  if (t_begin < t_end) fetch(t_begin, min(CHUNK, t_end - t_begin));
+  for (int t0 = t_begin; t0 < t_end; t0 += CHUNK) {
+    const int n = min(CHUNK, t_end - t0);
+    __syncthreads();                             // the chunk before has been read by everyone
+    stage();
     __syncthreads();
+    if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      const float vj = vs[tt * cols + jl];
-      const float* qt = qs + tt * dpad + l * (kScanDpt + 1);
-      const float* kt = ks + tt * dpad + l * (kScanDpt + 1);
-      const float* at = as + tt * dpad + l * (kScanDpt + 1);
+      const float vj = vs[tt * COLS + jl];
+      const float4* qt = reinterpret_cast<const float4*>(qs + tt * DPAD + l * kScanPad);
+      const float4* kt = reinterpret_cast<const float4*>(ks + tt * DPAD + l * kScanPad);
+      const float4* at = reinterpret_cast<const float4*>(as + tt * DPAD + l * kScanPad);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < kScanDpt; ++i) {
-        S[i] = fmaf(at[i], S[i], kt[i] * vj);
-        acc[i & 3] = fmaf(S[i], qt[i], acc[i & 3]);
+      for (int i = 0; i < kScanDpt / 4; ++i) {
+        const float4 a4 = at[i], k4 = kt[i], q4 = qt[i];
+        S[4 * i] = fmaf(a4.x, S[4 * i], k4.x * vj);
+        S[4 * i + 1] = fmaf(a4.y, S[4 * i + 1], k4.y * vj);
+        S[4 * i + 2] = fmaf(a4.z, S[4 * i + 2], k4.z * vj);
+        S[4 * i + 3] = fmaf(a4.w, S[4 * i + 3], k4.w * vj);
+        acc[0] = fmaf(S[4 * i], q4.x, acc[0]);
+        acc[1] = fmaf(S[4 * i + 1], q4.y, acc[1]);
+        acc[2] = fmaf(S[4 * i + 2], q4.z, acc[2]);
+        acc[3] = fmaf(S[4 * i + 3], q4.w, acc[3]);
       }
       float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      for (int w = lpc >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+#pragma unroll
+      for (int w = LPC >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
       if (l == 0 && col_ok) out[(size_t)(t0 + tt) * heads * vdim + hv + j] = o;
     }
   }
 #pragma unroll
   for (int i = 0; i < kScanDpt; i += 4) {
     const int c = l * kScanDpt + i;
-    if (vec) {
+    if (vec_state) {
       if (col_ok && c < dim) *reinterpret_cast<float4*>(S_g + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
     } else {
 #pragma unroll
@@ -156,58 +233,80 @@ __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict_
   }
 }
 
-ARLE_API int arle_gla_decay(const void* low, int dtype, int low_stride, const float* w2, const float* bias, float tau,
+ARLE_API int arle_gla_decay(const void* low, int dtype, int low_stride, const float* w2t, const float* bias, float tau,
                             float* alpha, int num_tokens, int channels, int rank, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
-  if (channels <= 0 || rank <= 0 || !(tau > 0.f) || rank > 8192) return ARLE_E_BADARG;
+  if (channels <= 0 || rank <= 0 || !(tau > 0.f) || rank > 1024) return ARLE_E_BADARG;
   const int threads = 256;
-  int by = (channels + threads - 1) / threads;
-  if (by > 64) by = 64;
-  const size_t smem = (size_t)rank * sizeof(float);
+  dim3 grid((num_tokens + kDecayTokens - 1) / kDecayTokens, (channels + threads - 1) / threads);
+  if (grid.y > 65535) return ARLE_E_UNSUPPORTED;
+  const size_t smem = (size_t)kDecayTokens * rank * sizeof(float);
   if (dtype == 0)
-    launch_kernel(gla_decay_kernel<float>, dim3(num_tokens, by), dim3(threads), smem, s, 1, (const float*)low, low_stride, w2, bias,
-                  1.0f / tau, alpha, channels, rank);
+    launch_kernel(gla_decay_kernel<float>, grid, dim3(threads), smem, s, 1, (const float*)low, low_stride, w2t, bias, 1.0f / tau, alpha,
+                  num_tokens, channels, rank);
   else if (dtype == 1)
-    launch_kernel(gla_decay_kernel<__nv_bfloat16>, dim3(num_tokens, by), dim3(threads), smem, s, 1, (const __nv_bfloat16*)low,
-                  low_stride, w2, bias, 1.0f / tau, alpha, channels, rank);
+    launch_kernel(gla_decay_kernel<__nv_bfloat16>, grid, dim3(threads), smem, s, 1, (const __nv_bfloat16*)low, low_stride, w2t, bias,
+                  1.0f / tau, alpha, num_tokens, channels, rank);
   else
     return ARLE_E_BADARG;
   return launch_status();
 }
 
-// Lanes that share a column of the state: the least power of two that gives every thread at most 16
-// key channels.
-static int scan_lanes_per_col(int dim) {
-  int lpc = 1;
-  while (lpc * kScanDpt < dim) lpc <<= 1;
-  return lpc;
+namespace {
+
+template <typename T, int LPC>
+int scan_launch(const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state, const int* q_indptr,
+                const int* state_slots, float* out, int rows, int heads, int dim, int vdim, float q_scale, cudaStream_t s) {
+  constexpr int COLS = kScanThreads / LPC;
+  dim3 grid((vdim + COLS - 1) / COLS, heads, rows);
+  const size_t eb = sizeof(T) * 4;               // bytes of four elements of q or k
+  const bool vec = dim % 4 == 0 && in_stride % 4 == 0 && ((uintptr_t)q % eb) == 0 && ((uintptr_t)k % eb) == 0 &&
+                   ((uintptr_t)alpha % 16) == 0;
+  if (vec)
+    launch_kernel(gla_scan_kernel<T, LPC, true>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v, in_stride,
+                  alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
+  else
+    launch_kernel(gla_scan_kernel<T, LPC, false>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v, in_stride,
+                  alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
+  return launch_status();
 }
 
+template <typename T>
+int scan_dispatch(int lpc, const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state,
+                  const int* q_indptr, const int* state_slots, float* out, int rows, int heads, int dim, int vdim, float q_scale,
+                  cudaStream_t s) {
+#define ARLE_SCAN(L) \
+  case L: return scan_launch<T, L>(q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s)
+  switch (lpc) {
+    ARLE_SCAN(1);
+    ARLE_SCAN(2);
+    ARLE_SCAN(4);
+    ARLE_SCAN(8);
+    ARLE_SCAN(16);
+    ARLE_SCAN(32);
+  }
+#undef ARLE_SCAN
+  return ARLE_E_UNSUPPORTED;
+}
+
+}  // namespace
+
+// Lanes that share a column of the state: the least power of two that gives every thread at most 16
+// key channels.  It depends on dim alone, so the order of a token's sums does too.
 ARLE_API int arle_gla_scan(const void* q, const void* k, const void* v, int dtype, int in_stride, const float* alpha,
                            float* state, const int* q_indptr, const int* state_slots, float* out, int rows, int heads,
                            int dim, int vdim, float q_scale, int max_q_len, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || max_q_len <= 0) return ARLE_E_BADARG;
   if (dim > 32 * kScanDpt || heads > 65535 || rows > 65535) return ARLE_E_UNSUPPORTED;
-  const int lpc = scan_lanes_per_col(dim);
-  const int cols = kScanThreads / lpc, dpad = (kScanDpt + 1) * lpc;
-  const int per_token = (3 * dpad + cols) * (int)sizeof(float);
-  int chunk = (40 * 1024) / per_token;
-  if (chunk > 16) chunk = 16;
-  if (chunk > max_q_len) chunk = max_q_len;
-  if (chunk < 1) chunk = 1;
-  const size_t smem = (size_t)chunk * per_token;
-  dim3 grid((vdim + cols - 1) / cols, heads, rows);
+  int lpc = 1;
+  while (lpc * kScanDpt < dim) lpc <<= 1;
   if (dtype == 0)
-    launch_kernel(gla_scan_kernel<float>, grid, dim3(kScanThreads), smem, s, 1, (const float*)q, (const float*)k, (const float*)v,
-                  in_stride, alpha, state, q_indptr, state_slots, out, heads, dim, vdim, lpc, chunk, q_scale);
-  else if (dtype == 1)
-    launch_kernel(gla_scan_kernel<__nv_bfloat16>, grid, dim3(kScanThreads), smem, s, 1, (const __nv_bfloat16*)q,
-                  (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, in_stride, alpha, state, q_indptr, state_slots, out, heads, dim,
-                  vdim, lpc, chunk, q_scale);
-  else
-    return ARLE_E_BADARG;
-  return launch_status();
+    return scan_dispatch<float>(lpc, q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s);
+  if (dtype == 1)
+    return scan_dispatch<__nv_bfloat16>(lpc, q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim,
+                                        q_scale, s);
+  return ARLE_E_BADARG;
 }
 
 ARLE_API int arle_gla_out(const float* o, const void* gate, int dtype, int gate_stride, const float* weight, float eps,

@@ -926,15 +926,16 @@ def logit_cap(logits, cap: float) -> None:
 
 
 # ------------------------------------------------------------ gated linear attention
-def gla_decay(low, w2, bias, tau: float, alpha) -> None:
-    """alpha[t, c] = sigmoid(bias[c] + sum_r low[t, r] * w2[c, r]) ^ (1 / tau), float32 [T, channels].  ``low``
-    [T, rank] in the activation type (a slice of a wider row is fine), w2 float32 [channels, rank], bias float32
-    [channels] or None."""
+def gla_decay(low, w2t, bias, tau: float, alpha) -> None:
+    """alpha[t, c] = sigmoid(bias[c] + sum_r low[t, r] * w2t[r, c]) ^ (1 / tau), float32 [T, channels].  ``low``
+    [T, rank] in the activation type (a slice of a wider row is fine), w2t float32 [rank, channels] (the gate's
+    second matrix transposed), bias float32 [channels] or None."""
     T, rank = low.shape
-    C = w2.shape[0]
-    if (w2.dtype != torch.float32 or w2.shape[1] != rank or not w2.is_contiguous() or alpha.dtype != torch.float32
+    C = w2t.shape[1]
+    w2 = w2t
+    if (w2.dtype != torch.float32 or w2.shape[0] != rank or not w2.is_contiguous() or alpha.dtype != torch.float32
             or tuple(alpha.shape) != (T, C) or not alpha.is_contiguous() or low.stride(1) != 1):
-        raise KernelError(f"gla_decay: shapes low {tuple(low.shape)} w2 {tuple(w2.shape)} alpha {tuple(alpha.shape)}")
+        raise KernelError(f"gla_decay: shapes low {tuple(low.shape)} w2t {tuple(w2.shape)} alpha {tuple(alpha.shape)}")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != C):
         raise KernelError("gla_decay: bias must be float32 [channels]")
     _check(library().arle_gla_decay(_ptr(low), _dt(low), low.stride(0), _ptr(w2), _ptr(bias), float(tau), _ptr(alpha), T, C,

@@ -85,7 +85,7 @@ class GatedLinearAttention(Mixer):
         o = tensors[self._name("o")]
         self.w_o = o.to(device=device, dtype=dtype if dtype == torch.bfloat16 else o.dtype).contiguous()
         # what enters the recurrence is float32 in both precisions
-        self.w_decay = tensors[self._name("decay_out")].to(device=device, dtype=torch.float32).contiguous()
+        self.w_decay = tensors[self._name("decay_out")].to(device=device, dtype=torch.float32).t().contiguous()   # [rank, heads*key_dim]
         self.decay_bias = tensors[self._name("decay_bias")].to(device=device, dtype=torch.float32).contiguous()
         self.norm = tensors[self._name("norm")].to(device=device, dtype=torch.float32).contiguous()
 

@@ -219,8 +219,8 @@ def logit_cap(logits, cap):
     logits.copy_(cap * torch.tanh(logits / cap))
 
 
-def gla_decay(low, w2, bias, tau, alpha):
-    z = low.to(F32) @ w2.t()
+def gla_decay(low, w2t, bias, tau, alpha):
+    z = low.to(F32) @ w2t
     if bias is not None:
         z = z + bias
     alpha.copy_(torch.exp(-torch.nn.functional.softplus(-z) / tau))

@@ -179,7 +179,7 @@ def test_recurrent_side_kernels(dtype, heads, dim, vdim, rank, tau):
         proj = (x.float() @ w_in.float().t()).to(dtype).to(DEV)
         ind = torch.tensor([0] + list(np.cumsum([r.shape[0] for r in rows])), dtype=torch.int32, device=DEV)
         alpha = torch.zeros(T, dq, device=DEV)
-        ops.gla_decay(proj[:, 2 * dq + 2 * dv:], w["p.a2"].float().to(DEV), w["p.a2.b"].float().to(DEV), tau, alpha)
+        ops.gla_decay(proj[:, 2 * dq + 2 * dv:], w["p.a2"].float().t().contiguous().to(DEV), w["p.a2.b"].float().to(DEV), tau, alpha)
         a_want = plain.decay(x.double(), w, "p.", m).reshape(T, dq)
         assert (alpha.cpu().double() - a_want).abs().max() < (2e-6 if dtype == torch.float32 else 2e-2)
         o = torch.zeros(T, dv, device=DEV)
