@@ -12,7 +12,8 @@
 // Rotation, within the first rotary_dim elements of each head: pairing 0 turns element i with
 // i + rotary_dim/2 ("half split"), pairing 1 turns element 2i with 2i + 1 ("interleaved"); the
 // pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a) with a = position * inv_freq[i],
-// in float32 (sincosf).  Norm statistics and products are float32.
+// in float32 (sincosf), or with the cosines and sines of a table [T][rotary_dim/2] of (cos, sin) that was filled the
+// same way once for the step (the same bits).  Norm statistics and products are float32.
 // Cache layout: [page][kv_head][slot_in_page][head_dim]; slot_mapping[t] < 0: no store.
 #include "common.cuh"
 using namespace arle;
@@ -21,8 +22,8 @@ template <typename T>
 __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, const int* __restrict__ positions,
                                           const int* __restrict__ slot_mapping, const float* __restrict__ q_weight,
                                           const float* __restrict__ k_weight, float eps,
-                                          const float* __restrict__ inv_freq, int rotary_dim, int pairing,
-                                          int values_are_keys, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          const float* __restrict__ inv_freq, const float2* __restrict__ angles,
+                                          int rotary_dim, int pairing, int values_are_keys, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                           int nq, int nkv, int hd, int page_size) {
   pdl_launch_dependents();
   pdl_wait();
@@ -52,42 +53,49 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
   const int slot = nkv > 0 ? slot_mapping[t] : -1;
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
   const float pos = (float)positions[t];
-  const int half = rotary_dim >> 1;
-  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
-    const int head = e / hd, d = e - head * hd;
-    float o = row[e];
-    if (d < rotary_dim) {
-      int i, partner;
-      bool first;
-      if (pairing == 0) {
-        first = d < half;
-        i = first ? d : d - half;
-        partner = first ? e + half : e - half;
-      } else {
-        first = (d & 1) == 0;
-        i = d >> 1;
-        partner = first ? e + 1 : e - 1;
-      }
+  const int half = rotary_dim >> 1, hd2 = hd >> 1;
+  const float2* ang = angles ? angles + (size_t)t * half : nullptr;
+  // a thread takes a pair of elements: the two that turn together, or two neighbours past rotary_dim
+  for (int p = threadIdx.x; p < (nq + nkv) * hd2; p += blockDim.x) {
+    const int head = p / hd2, d2 = p - head * hd2;
+    int e0, e1;
+    float o0, o1;
+    if (d2 < half) {
+      e0 = head * hd + (pairing == 0 ? d2 : 2 * d2);
+      e1 = pairing == 0 ? e0 + half : e0 + 1;
       float sn, cs;
-      sincosf(pos * inv_freq[i], &sn, &cs);
-      o = first ? row[e] * cs - row[partner] * sn : row[e] * cs + row[partner] * sn;
+      if (ang) {
+        const float2 a = ang[d2];
+        cs = a.x, sn = a.y;
+      } else {
+        sincosf(pos * inv_freq[d2], &sn, &cs);
+      }
+      o0 = row[e0] * cs - row[e1] * sn;
+      o1 = row[e1] * cs + row[e0] * sn;
+    } else {
+      e0 = head * hd + rotary_dim + 2 * (d2 - half);
+      e1 = e0 + 1;
+      o0 = row[e0], o1 = row[e1];
     }
-    if (e < nqe) {
-      src[e] = from_f32<T>(o);
+    if (head < nq) {
+      src[e0] = from_f32<T>(o0);
+      src[e1] = from_f32<T>(o1);
     } else if (slot >= 0) {
-      const int kvh = head - nq;
-      const size_t at = (((size_t)page * nkv + kvh) * page_size + off) * hd + d;
-      k_cache[at] = from_f32<T>(o);
-      v_cache[at] = values_are_keys ? src[e] : src[e + nke];
+      const size_t base = (((size_t)page * nkv + (head - nq)) * page_size + off) * hd - (size_t)head * hd;
+      k_cache[base + e0] = from_f32<T>(o0);
+      k_cache[base + e1] = from_f32<T>(o1);
+      v_cache[base + e0] = values_are_keys ? src[e0] : src[e0 + nke];
+      v_cache[base + e1] = values_are_keys ? src[e1] : src[e1 + nke];
     }
   }
 }
 
 ARLE_API int arle_attention_prep_row(void* qk, int dtype, int row_stride, const int* positions, const int* slot_mapping,
                                      const float* q_weight, const float* k_weight, float eps, const float* inv_freq,
-                                     int rotary_dim, int pairing, int values_are_keys, void* k_cache, void* v_cache, int nq,
+                                     const float* angles, int rotary_dim, int pairing, int values_are_keys, void* k_cache, void* v_cache, int nq,
                                      int nkv, int hd, int page_size, int num_tokens, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
+  if (hd & 1) return ARLE_E_UNSUPPORTED;
   if (hd <= 0 || nq <= 0 || nkv < 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return ARLE_E_BADARG;
   if (pairing != 0 && pairing != 1) return ARLE_E_BADARG;
   if (rotary_dim > 0 && !inv_freq) return ARLE_E_BADARG;
@@ -99,13 +107,14 @@ ARLE_API int arle_attention_prep_row(void* qk, int dtype, int row_stride, const 
   if (dtype == 0) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(attention_prep_row_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(attention_prep_row_kernel<float>, dim3(num_tokens), dim3(threads), smem, s, 1, (float*)qk, row_stride, positions,
-                  slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys, (float*)k_cache,
+                  slot_mapping, q_weight, k_weight, eps, inv_freq, (const float2*)angles, rotary_dim, pairing, values_are_keys, (float*)k_cache,
                   (float*)v_cache, nq, nkv, hd, page_size);
   } else if (dtype == 1) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(attention_prep_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(attention_prep_row_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), smem, s, 1, (__nv_bfloat16*)qk,
-                  row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys,
+                  row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, (const float2*)angles, rotary_dim, pairing,
+                  values_are_keys,
                   (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, hd, page_size);
   } else {
     return ARLE_E_BADARG;

@@ -19,7 +19,29 @@ __global__ void head_gate_kernel(const T* __restrict__ x, int x_stride, const T*
     const size_t t = idx / width;
     const int e = (int)(idx - t * width);
     const float s = g ? 1.0f / (1.0f + expf(-to_f32(g[t * g_stride + e / hd]))) : 1.0f;
-    out[t * out_stride + e] = from_f32<T>(to_f32(x[t * x_stride + e]) * s * scale);
+    out[t * out_stride + e] = from_f32<T>(to_f32(x[t * x_stride + e]) * (s * scale));
+  }
+}
+
+// Eight consecutive elements (of one head) per thread: bfloat16 rows whose head size is a multiple of 8 and whose
+// rows start on 16-byte boundaries.
+__global__ void head_gate_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ g,
+                                          int g_stride, float scale, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
+                                          int hd, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int w8 = heads * hd / 8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / w8;
+    const int e = (int)(idx - t * w8) * 8;
+    const float s = (g ? 1.0f / (1.0f + expf(-__bfloat162float(g[t * g_stride + e / hd]))) : 1.0f) * scale;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + t * x_stride + e);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(__low2float(h[i]) * s, __high2float(h[i]) * s);
+    *reinterpret_cast<uint4*>(out + t * out_stride + e) = o4;
   }
 }
 
@@ -51,6 +73,11 @@ ARLE_API int arle_head_gate(const void* x, int x_stride, const void* g, int g_st
   if (heads <= 0 || hd <= 0) return ARLE_E_BADARG;
   const size_t total = (size_t)num_tokens * heads * hd;
   const int threads = 256;
+  if (dtype == 1 && hd % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    launch_kernel(head_gate_bf16_vec_kernel, dim3(blocks_for(total / 8, threads)), dim3(threads), 0, s, 1, (const __nv_bfloat16*)x,
+                  x_stride, (const __nv_bfloat16*)g, g_stride, scale, (__nv_bfloat16*)out, out_stride, heads, hd, total / 8);
+    return launch_status();
+  }
   if (dtype == 0)
     launch_kernel(head_gate_kernel<float>, dim3(blocks_for(total, threads)), dim3(threads), 0, s, 1, (const float*)x, x_stride,
                   (const float*)g, g_stride, scale, (float*)out, out_stride, heads, hd, total);

@@ -10,9 +10,9 @@
 //    exp(-softplus(-z) / tau) in float32; a block takes eight tokens and 256 channels, r ascending.
 //  * gla_scan: the recurrence over this step's tokens of every request row, from the state that the
 //    request's slot holds, which is left updated.  Float32 throughout; q, k, v are read in the
-//    activation type.  One block per (columns of vdim, head, row); a thread keeps 16 consecutive key
-//    channels of one column of S in registers (lanes_per_col consecutive lanes share a column; the state
-//    is stored [vdim][dim] so that these are 64 contiguous bytes), the step's
+//    activation type.  One block of 512 threads per (columns of vdim, head, row); a thread keeps four
+//    consecutive key channels of one column of S in registers (up to 32 consecutive lanes share a column; the
+//    state is stored [vdim][dim], so a column's lanes read one contiguous run), the step's
 //    q, k, alpha and v are staged in shared memory a chunk of tokens at a time, and o_t[j] is the sum
 //    over the column's lanes.  The order of every sum depends on (dim, vdim) only: a token's result
 //    does not depend on how the prompt was cut or on what else is in the batch.
@@ -21,9 +21,7 @@
 #include "common.cuh"
 using namespace arle;
 
-constexpr int kScanThreads = 128;
-constexpr int kScanDpt = 16;                     // key channels per thread
-constexpr int kScanPad = 20;                     // floats a thread's 16 channels take in shared memory (16-byte rows, spread over the banks)
+constexpr int kScanThreads = 512;
 constexpr int kDecayTokens = 8;                  // tokens a block of the decay kernel takes
 
 // w2t is the second matrix of the gate transposed, [rank][channels]: consecutive threads read consecutive floats.
@@ -46,6 +44,7 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ lo
   float z[kDecayTokens];
 #pragma unroll
   for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = 0.f;
+#pragma unroll 8
   for (int r = 0; r < rank; ++r) {
     const float w = w2t[(size_t)r * channels + c];
 #pragma unroll
@@ -68,10 +67,11 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
   return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
 
-// LPC: lanes that share a column of the state (a power of two; LPC * 16 >= dim).  VEC: four channels at a time can be
-// fetched with one aligned load.  A chunk of CHUNK tokens is staged in shared memory; while it is worked on, the next
+// DPT: consecutive key channels of one column of the state that a thread keeps (4 up to 128 channels, then 8, 16).
+// LPC: lanes that share a column (a power of two; LPC * DPT >= dim).  VEC: four channels at a time can be fetched
+// with one aligned load.  A chunk of CHUNK tokens is staged in shared memory; while it is worked on, the next
 // chunk's q, k, alpha and v are already on their way into registers.
-template <typename T, int LPC, bool VEC>
+template <typename T, int DPT, int LPC, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
     const float* __restrict__ alpha, float* __restrict__ state, const int* __restrict__ q_indptr,
@@ -79,12 +79,13 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
   pdl_launch_dependents();
   pdl_wait();
   constexpr int COLS = kScanThreads / LPC;
-  constexpr int DSPAN = kScanDpt * LPC;          // dim rounded up; channels past dim hold zeros
-  constexpr int DPAD = kScanPad * LPC;
-  constexpr int CHUNK = LPC >= 8 ? 128 / LPC : 16;               // 16 tokens (8 and 4 for the widest heads)
-  constexpr int QUADS = CHUNK * DSPAN / 4;                       // groups of four channels in a chunk
-  constexpr int QPT = (QUADS + kScanThreads - 1) / kScanThreads;             // per thread: at most four
-  constexpr int VPT = (CHUNK * COLS + kScanThreads - 1) / kScanThreads;      // values per thread
+  constexpr int DSPAN = DPT * LPC;               // dim rounded up; channels past dim hold zeros
+  constexpr int PAD = DPT == 4 ? 4 : DPT + 4;    // floats a thread's channels take in shared memory: 16-byte rows, spread over the banks
+  constexpr int DPAD = PAD * LPC;
+  constexpr int CHUNK = DSPAN >= 512 ? 4 : (DSPAN >= 256 ? 8 : 16);
+  constexpr int QUADS = CHUNK * DSPAN / 4;       // groups of four channels in a chunk
+  constexpr int QPT = (QUADS + kScanThreads - 1) / kScanThreads;
+  constexpr int VPT = (CHUNK * COLS + kScanThreads - 1) / kScanThreads;
   __shared__ __align__(16) float qs[CHUNK * DPAD], ks[CHUNK * DPAD], as[CHUNK * DPAD];
   __shared__ float vs[CHUNK * COLS];
   const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * COLS;
@@ -92,13 +93,13 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
   const int j = j0 + jl;
   const bool col_ok = j < vdim;
   const int t_begin = q_indptr[r], t_end = q_indptr[r + 1];
-  // the state of a head is kept as [vdim][dim]: a thread's 16 channels of its column are contiguous
-  float* S_g = state + (((size_t)state_slots[r] * heads + h) * vdim + (col_ok ? j : 0)) * dim + l * kScanDpt;
+  // the state of a head is kept as [vdim][dim]: a thread's channels of its column are contiguous
+  float* S_g = state + (((size_t)state_slots[r] * heads + h) * vdim + (col_ok ? j : 0)) * dim + l * DPT;
   const bool vec_state = (dim & 3) == 0;
-  float S[kScanDpt];
+  float S[DPT];
 #pragma unroll
-  for (int i = 0; i < kScanDpt; i += 4) {
-    const int c = l * kScanDpt + i;
+  for (int i = 0; i < DPT; i += 4) {
+    const int c = l * DPT + i;
     if (vec_state) {
       float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
       if (col_ok && c < dim) u = *reinterpret_cast<const float4*>(S_g + i);
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     for (int u = 0; u < QPT; ++u) {
       const int idx = threadIdx.x + u * kScanThreads;
       const int tt = idx / (DSPAN / 4), c = (idx - tt * (DSPAN / 4)) * 4;
-      const int at = tt * DPAD + (c / kScanDpt) * kScanPad + (c % kScanDpt);
+      const int at = tt * DPAD + (c / DPT) * PAD + (c % DPT);
       if (idx >= QUADS) continue;
       *reinterpret_cast<float4*>(qs + at) = make_float4(rq[u].x * q_scale, rq[u].y * q_scale, rq[u].z * q_scale, rq[u].w * q_scale);
       *reinterpret_cast<float4*>(ks + at) = rk[u];
@@ -171,12 +172,12 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
 #pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       const float vj = vs[tt * COLS + jl];
-      const float4* qt = reinterpret_cast<const float4*>(qs + tt * DPAD + l * kScanPad);
-      const float4* kt = reinterpret_cast<const float4*>(ks + tt * DPAD + l * kScanPad);
-      const float4* at = reinterpret_cast<const float4*>(as + tt * DPAD + l * kScanPad);
+      const float4* qt = reinterpret_cast<const float4*>(qs + tt * DPAD + l * PAD);
+      const float4* kt = reinterpret_cast<const float4*>(ks + tt * DPAD + l * PAD);
+      const float4* at = reinterpret_cast<const float4*>(as + tt * DPAD + l * PAD);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < kScanDpt / 4; ++i) {
+      for (int i = 0; i < DPT / 4; ++i) {
         const float4 a4 = at[i], k4 = kt[i], q4 = qt[i];
         S[4 * i] = fmaf(a4.x, S[4 * i], k4.x * vj);
         S[4 * i + 1] = fmaf(a4.y, S[4 * i + 1], k4.y * vj);
@@ -194,8 +195,8 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     }
   }
 #pragma unroll
-  for (int i = 0; i < kScanDpt; i += 4) {
-    const int c = l * kScanDpt + i;
+  for (int i = 0; i < DPT; i += 4) {
+    const int c = l * DPT + i;
     if (vec_state) {
       if (col_ok && c < dim) *reinterpret_cast<float4*>(S_g + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
     } else {
@@ -254,7 +255,7 @@ ARLE_API int arle_gla_decay(const void* low, int dtype, int low_stride, const fl
 
 namespace {
 
-template <typename T, int LPC>
+template <typename T, int DPT, int LPC>
 int scan_launch(const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state, const int* q_indptr,
                 const int* state_slots, float* out, int rows, int heads, int dim, int vdim, float q_scale, cudaStream_t s) {
   constexpr int COLS = kScanThreads / LPC;
@@ -263,49 +264,46 @@ int scan_launch(const void* q, const void* k, const void* v, int in_stride, cons
   const bool vec = dim % 4 == 0 && in_stride % 4 == 0 && ((uintptr_t)q % eb) == 0 && ((uintptr_t)k % eb) == 0 &&
                    ((uintptr_t)alpha % 16) == 0;
   if (vec)
-    launch_kernel(gla_scan_kernel<T, LPC, true>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v, in_stride,
-                  alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
+    launch_kernel(gla_scan_kernel<T, DPT, LPC, true>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v,
+                  in_stride, alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
   else
-    launch_kernel(gla_scan_kernel<T, LPC, false>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v, in_stride,
-                  alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
+    launch_kernel(gla_scan_kernel<T, DPT, LPC, false>, grid, dim3(kScanThreads), 0, s, 1, (const T*)q, (const T*)k, (const T*)v,
+                  in_stride, alpha, state, q_indptr, state_slots, out, heads, dim, vdim, q_scale);
   return launch_status();
 }
 
+// The split of the key channels among threads depends on dim alone, so the order of a token's sums does too: four
+// channels a thread up to 128 channels (as many lanes as that takes, a power of two), then 8 and 16 on 32 lanes.
 template <typename T>
-int scan_dispatch(int lpc, const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state,
+int scan_dispatch(const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state,
                   const int* q_indptr, const int* state_slots, float* out, int rows, int heads, int dim, int vdim, float q_scale,
                   cudaStream_t s) {
-#define ARLE_SCAN(L) \
-  case L: return scan_launch<T, L>(q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s)
-  switch (lpc) {
-    ARLE_SCAN(1);
-    ARLE_SCAN(2);
-    ARLE_SCAN(4);
-    ARLE_SCAN(8);
-    ARLE_SCAN(16);
-    ARLE_SCAN(32);
-  }
+#define ARLE_SCAN(D, L) \
+  return scan_launch<T, D, L>(q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s)
+  if (dim <= 4) ARLE_SCAN(4, 1);
+  if (dim <= 8) ARLE_SCAN(4, 2);
+  if (dim <= 16) ARLE_SCAN(4, 4);
+  if (dim <= 32) ARLE_SCAN(4, 8);
+  if (dim <= 64) ARLE_SCAN(4, 16);
+  if (dim <= 128) ARLE_SCAN(4, 32);
+  if (dim <= 256) ARLE_SCAN(8, 32);
+  if (dim <= 512) ARLE_SCAN(16, 32);
 #undef ARLE_SCAN
   return ARLE_E_UNSUPPORTED;
 }
 
 }  // namespace
 
-// Lanes that share a column of the state: the least power of two that gives every thread at most 16
-// key channels.  It depends on dim alone, so the order of a token's sums does too.
 ARLE_API int arle_gla_scan(const void* q, const void* k, const void* v, int dtype, int in_stride, const float* alpha,
                            float* state, const int* q_indptr, const int* state_slots, float* out, int rows, int heads,
                            int dim, int vdim, float q_scale, int max_q_len, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || max_q_len <= 0) return ARLE_E_BADARG;
-  if (dim > 32 * kScanDpt || heads > 65535 || rows > 65535) return ARLE_E_UNSUPPORTED;
-  int lpc = 1;
-  while (lpc * kScanDpt < dim) lpc <<= 1;
+  if (dim > 512 || heads > 65535 || rows > 65535) return ARLE_E_UNSUPPORTED;
   if (dtype == 0)
-    return scan_dispatch<float>(lpc, q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s);
+    return scan_dispatch<float>(q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s);
   if (dtype == 1)
-    return scan_dispatch<__nv_bfloat16>(lpc, q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim,
-                                        q_scale, s);
+    return scan_dispatch<__nv_bfloat16>(q, k, v, in_stride, alpha, state, q_indptr, state_slots, out, rows, heads, dim, vdim, q_scale, s);
   return ARLE_E_BADARG;
 }
 

@@ -44,7 +44,7 @@ _SIGNATURES = {
     "arle_residual_add": [_P, _P, _I, _I, _I, _P],
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
     "arle_act_mul": [_P, _P, _I, _I, _I, _I, _P],
-    "arle_attention_prep_row": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_attention_prep_row": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_head_gate": [_P, _I, _P, _I, _F, _P, _I, _I, _I, _I, _I, _P],
     "arle_weighted_sum": [_P, _F, _P, _F, _P, _I, ctypes.c_longlong, _P],
     "arle_logit_cap": [_P, _F, ctypes.c_longlong, _P],
@@ -865,13 +865,17 @@ ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
 
 
 def attention_prep_row(qk, positions, slot_mapping, q_weight, k_weight, eps: float, inv_freq, rotary_dim: int, pairing: str,
-                       values_are_keys: bool, k_cache, v_cache, nq: int, nkv: int, hd: int, page_size: int) -> None:
+                       values_are_keys: bool, k_cache, v_cache, nq: int, nkv: int, hd: int, page_size: int, angles=None) -> None:
     """RMSNorm of q and of k over their whole projected rows (weights float32 [nq*hd], [nkv*hd], or None: no
     norm), rotation of the first ``rotary_dim`` elements of every head (``pairing`` "half": element i with
     i + rotary_dim/2; "interleaved": 2i with 2i + 1), q stored in place on qk [T, >= (nq + nkv) hd], k into the
     paged k_cache; v_cache gets the keys as projected (``values_are_keys``) or the v heads that follow the k
-    heads in the row.  nkv = 0: queries only, nothing stored."""
+    heads in the row.  nkv = 0: queries only, nothing stored.  ``angles``: the table of ``rotary_angles`` for these
+    positions and inv_freq (float32 [T, rotary_dim / 2, 2]), or None: the kernel evaluates them itself (the same bits)."""
     T = qk.shape[0]
+    if angles is not None and (angles.dtype != torch.float32 or tuple(angles.shape) != (T, rotary_dim // 2, 2)
+                               or not angles.is_contiguous()):
+        raise KernelError("attention_prep_row: angles must be contiguous float32 [T, rotary_dim / 2, 2]")
     need = (nq + (nkv if values_are_keys else 2 * nkv)) * hd
     if qk.stride(1) != 1 or qk.shape[1] < need:
         raise KernelError(f"attention_prep_row: qk must be [T, >= {need}] with unit inner stride")
@@ -892,7 +896,8 @@ def attention_prep_row(qk, positions, slot_mapping, q_weight, k_weight, eps: flo
         raise KernelError("attention_prep_row: inv_freq must be float32 [rotary_dim / 2]")
     _check(library().arle_attention_prep_row(
         _ptr(qk), _dt(qk), qk.stride(0), _ptr(positions), _ptr(slot_mapping) if nkv else None, _ptr(q_weight), _ptr(k_weight),
-        float(eps), _ptr(inv_freq) if rotary_dim else None, int(rotary_dim), ROTARY_PAIRINGS[pairing], int(bool(values_are_keys)),
+        float(eps), _ptr(inv_freq) if rotary_dim else None, _ptr(angles) if rotary_dim else None, int(rotary_dim),
+        ROTARY_PAIRINGS[pairing], int(bool(values_are_keys)),
         _ptr(k_cache) if nkv else None, _ptr(v_cache) if nkv else None, nq, nkv, hd, page_size, T, _stream()),
         "attention_prep_row")
 

@@ -127,10 +127,11 @@ class Attention(Mixer):
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
-    def _angles(self, qkv, ctx, inv_freq, rdim):
+    def _angles(self, qkv, ctx, inv_freq, rdim, general=False):
         """Cosines and sines of the step's positions, evaluated once for all layers that rotate by the same
-        frequencies (kept in the step's memo under the encoding's description)."""
-        if not rdim or not ops.attention_prep_takes_angles(qkv, self.spec.head_dim, rdim):
+        frequencies (kept in the step's memo under the encoding's description).  The general preparation takes the
+        table for any head size, from 32 tokens on."""
+        if not rdim or not (qkv.shape[0] >= 32 if general else ops.attention_prep_takes_angles(qkv, self.spec.head_dim, rdim)):
             return None
         key = ("rotary_angles", getattr(self.position, "spec", None) or id(self.position))
         angles = ctx.memo.get(key)
@@ -166,7 +167,8 @@ class Attention(Mixer):
         else:
             ops.attention_prep_row(proj, ctx.positions, cache.slot_mapping if kv else None, self.q_norm,
                                    self.k_norm if kv else None, eps, inv_freq, rdim, self.pairing, s.values == "keys",
-                                   cache.k if kv else None, cache.v if kv else None, nq, kv, hd, cache.page_size)
+                                   cache.k if kv else None, cache.v if kv else None, nq, kv, hd, cache.page_size,
+                                   angles=self._angles(proj, ctx, inv_freq, rdim, general=True))
         attn = ctx.ws.get("attn_out", (T, nq * hd), x.dtype)
         ops.paged_attention(proj[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token,
                             cache.block_table, nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx)

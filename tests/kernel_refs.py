@@ -171,7 +171,7 @@ def gemm_act_mul(x, w, gate_up, out, activation="silu"):
 
 
 def attention_prep_row(qk, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, pairing, values_are_keys,
-                       k_cache, v_cache, nq, nkv, hd, page_size):
+                       k_cache, v_cache, nq, nkv, hd, page_size, angles=None):
     T = qk.shape[0]
 
     def norm_rope(x, w, heads):
@@ -249,5 +249,10 @@ def gla_out(o, gate, weight, eps, scale, out, heads, vdim):
     out.copy_((y * scale).to(out.dtype))
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample",
+def rotary_angles(positions, inv_freq, out):
+    ang = positions.to(F32)[:, None] * inv_freq[None, :]
+    out.copy_(torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1))
+
+
+ALL = ("rotary_angles", "embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample",
        "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out")
