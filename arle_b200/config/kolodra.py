@@ -96,12 +96,15 @@ class KolodraConfig:
             m = e.get("mixer")
             if not isinstance(m, dict) or not isinstance(m.get("left"), dict) or not isinstance(m.get("right"), dict):
                 raise ConfigError(f"config.json: {w}.mixer needs 'left' and 'right'")
-            src = e.get("weights_of")
-            if src is not None:
+            src, hops = e.get("weights_of"), 0
+            while src is not None:                    # a layer may name a layer that itself names another
                 if isinstance(src, bool) or not isinstance(src, int) or not 0 <= src < len(entries) or src == i:
                     raise ConfigError(f"config.json: {w}.weights_of = {src!r} names no other layer")
-                if entries[src].get("weights_of") is not None:
-                    raise ConfigError(f"config.json: {w}.weights_of names layer {src}, which has no tensors of its own")
+                if not isinstance(entries[src], dict) or entries[src].get("weights_of") is None:
+                    break
+                src, hops = entries[src]["weights_of"], hops + 1
+                if hops > len(entries):
+                    raise ConfigError(f"config.json: {w}.weights_of leads in a circle")
             lh, lk, ld = _pos_int(m, "left.heads"), _pos_int(m, "left.kv_heads"), _pos_int(m, "left.dim")
             if lh % lk:
                 raise ConfigError(f"config.json: {w}.mixer.left.heads ({lh}) must be a multiple of kv_heads ({lk})")
@@ -147,7 +150,8 @@ class KolodraConfig:
             raise ConfigError(f"config.json: 'logit_softcap' must be a positive number or null, got {cap!r}")
         eos = d.get("eos_token_id")
         stops = (eos,) if isinstance(eos, int) and not isinstance(eos, bool) else tuple(int(x) for x in eos) if isinstance(eos, list) else ()
-        return cls(vocab=_pos_int(d, "vocab"), width=_pos_int(d, "width"), embedding_scale=float(_get(d, "embedding.scale")),
+        scale = float(_get(d, "embedding.scale")) if isinstance(d.get("embedding"), dict) and "scale" in d["embedding"] else 1.0
+        return cls(vocab=_pos_int(d, "vocab"), width=_pos_int(d, "width"), embedding_scale=scale,
                    norm_eps=eps, logit_softcap=float(cap) if cap is not None else None, layers=tuple(layers),
                    max_position=_pos_int(d, "max_position") if "max_position" in d else 1 << 20,
                    bos_token_id=d.get("bos_token_id") if isinstance(d.get("bos_token_id"), int) else None,

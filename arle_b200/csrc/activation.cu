@@ -10,7 +10,7 @@ __device__ __forceinline__ float gelu_tanh_f(float g) {
 }
 
 template <typename T, int ACT>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int out_stride) {
   pdl_launch_dependents();
   pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -19,14 +19,14 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     const int i = (int)(idx - t * inter);
     const float g = to_f32(gu[t * 2 * (size_t)inter + 2 * i]);
     const float u = to_f32(gu[t * 2 * (size_t)inter + 2 * i + 1]);
-    out[idx] = from_f32<T>((ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh_f(g)) * u);
+    out[t * out_stride + i] = from_f32<T>((ACT == 0 ? g / (1.0f + expf(-g)) : gelu_tanh_f(g)) * u);
   }
 }
 
 // Eight elements per thread and step for bfloat16 rows whose width is a multiple of 8.
 template <int ACT>
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
-                                         size_t total8) {
+                                         size_t total8, int out_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int i8 = inter >> 3;
@@ -51,27 +51,27 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, _
       else
         o2[k] = __floats2bfloat162_rn(gelu_tanh_f(ga) * __high2float(p0), gelu_tanh_f(gb) * __high2float(p1));
     }
-    *reinterpret_cast<uint4*>(out + t * (size_t)inter + 8 * c) = o4;
+    *reinterpret_cast<uint4*>(out + t * (size_t)out_stride + 8 * c) = o4;
   }
 }
 
 template <int ACT>
-static int act_mul_launch(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
+static int act_mul_launch(const void* gu, void* out, int dtype, int num_tokens, int inter, int out_stride, cudaStream_t s) {
   const size_t total = (size_t)num_tokens * inter;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  if (dtype == 1 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+  if (dtype == 1 && inter % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const size_t total8 = total / 8;
     size_t b8 = (total8 + threads - 1) / threads;
     if (b8 > 148 * 32) b8 = 148 * 32;
-    launch_kernel(silu_mul_bf16_vec_kernel<ACT>, dim3((int)b8), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
+    launch_kernel(silu_mul_bf16_vec_kernel<ACT>, dim3((int)b8), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8, out_stride);
     return launch_status();
   }
   if (dtype == 0)
-    launch_kernel(silu_mul_kernel<float, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, inter, total);
+    launch_kernel(silu_mul_kernel<float, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, inter, total, out_stride);
   else if (dtype == 1)
-    launch_kernel(silu_mul_kernel<__nv_bfloat16, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    launch_kernel(silu_mul_kernel<__nv_bfloat16, ACT>, dim3((int)blocks), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total, out_stride);
   else
     return ARLE_E_BADARG;
   return launch_status();
@@ -80,12 +80,14 @@ static int act_mul_launch(const void* gu, void* out, int dtype, int num_tokens, 
 ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (inter <= 0) return ARLE_E_BADARG;
-  return act_mul_launch<0>(gu, out, dtype, num_tokens, inter, s);
+  return act_mul_launch<0>(gu, out, dtype, num_tokens, inter, inter, s);
 }
 
-// act: 0 silu, 1 gelu (tanh form)
-ARLE_API int arle_act_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, int act, cudaStream_t s) {
+// act: 0 silu, 1 gelu (tanh form); out_stride: elements between rows of out (inter when it is contiguous)
+ARLE_API int arle_act_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, int act, int out_stride,
+                          cudaStream_t s) {
   if (num_tokens <= 0) return 0;
-  if (inter <= 0 || (act != 0 && act != 1)) return ARLE_E_BADARG;
-  return act == 0 ? act_mul_launch<0>(gu, out, dtype, num_tokens, inter, s) : act_mul_launch<1>(gu, out, dtype, num_tokens, inter, s);
+  if (inter <= 0 || (act != 0 && act != 1) || out_stride < inter) return ARLE_E_BADARG;
+  return act == 0 ? act_mul_launch<0>(gu, out, dtype, num_tokens, inter, out_stride, s)
+                  : act_mul_launch<1>(gu, out, dtype, num_tokens, inter, out_stride, s);
 }

@@ -3,7 +3,7 @@
 //
 // Input row t of qk: [q heads (nq * hd) | k heads (nkv * hd) | ...] (row stride given).
 // One block per token:
-//   q: x <- x * rsqrt(mean over all nq*hd elements of x^2 + eps) * q_weight[e] (if q_weight),
+//   q: x <- x * q_weight[e] * rsqrt(mean over all nq*hd elements of x^2 + eps) (if q_weight),
 //      rotate, store in place;
 //   k: the same over the nkv*hd elements with k_weight, rotate, store into k_cache at the
 //      token's slot;
@@ -27,32 +27,39 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
                                           int nq, int nkv, int hd, int page_size) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float row[];                 // (nq + nkv) * hd floats
-  __shared__ float red[33];
+  extern __shared__ float row[];                 // (nq + nkv) * hd floats: x * weight, still without the row's factor
+  __shared__ float red[2][33];
   const int t = blockIdx.x;
   const int nqe = nq * hd, nke = nkv * hd;
   T* src = qk + (size_t)t * row_stride;
+  // everything the block needs from memory is asked for before the first use
+  const int slot = nkv > 0 ? slot_mapping[t] : -1;
+  const float pos = (float)positions[t];
   float sq = 0.f, sk = 0.f;
   for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
     const float x = to_f32(src[e]);
-    row[e] = x;
+    const float* wt = e < nqe ? q_weight : k_weight;
+    const float w = wt ? wt[e < nqe ? e : e - nqe] : 1.0f;
+    row[e] = x * w;
     if (e < nqe) sq += x * x; else sk += x * x;
   }
-  sq = block_sum(sq, red);
-  sk = block_sum(sk, red);
+  {                                              // both sums in one pass over the block
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) red[0][warp] = sq, red[1][warp] = sk;
+    __syncthreads();                             // also: every row[] entry is written
+    if (warp < 2) {
+      float v = lane < nwarps ? red[warp][lane] : 0.f;
+      v = warp_sum(v);
+      if (lane == 0) red[warp][32] = v;
+    }
+    __syncthreads();
+    sq = red[0][32], sk = red[1][32];
+  }
   const float inv_q = q_weight ? 1.0f / sqrtf(sq / (float)nqe + eps) : 1.0f;
   const float inv_k = k_weight ? 1.0f / sqrtf(sk / (float)(nke > 0 ? nke : 1) + eps) : 1.0f;
-  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
-    if (e < nqe) {
-      if (q_weight) row[e] = row[e] * inv_q * q_weight[e];
-    } else if (k_weight) {
-      row[e] = row[e] * inv_k * k_weight[e - nqe];
-    }
-  }
-  __syncthreads();
-  const int slot = nkv > 0 ? slot_mapping[t] : -1;
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
-  const float pos = (float)positions[t];
   const int half = rotary_dim >> 1, hd2 = hd >> 1;
   const float2* ang = angles ? angles + (size_t)t * half : nullptr;
   // a thread takes a pair of elements: the two that turn together, or two neighbours past rotary_dim
@@ -70,12 +77,15 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
       } else {
         sincosf(pos * inv_freq[d2], &sn, &cs);
       }
-      o0 = row[e0] * cs - row[e1] * sn;
-      o1 = row[e1] * cs + row[e0] * sn;
+      const float inv = head < nq ? inv_q : inv_k;
+      const float x0 = row[e0] * inv, x1 = row[e1] * inv;
+      o0 = x0 * cs - x1 * sn;
+      o1 = x1 * cs + x0 * sn;
     } else {
+      const float inv = head < nq ? inv_q : inv_k;
       e0 = head * hd + rotary_dim + 2 * (d2 - half);
       e1 = e0 + 1;
-      o0 = row[e0], o1 = row[e1];
+      o0 = row[e0] * inv, o1 = row[e1] * inv;
     }
     if (head < nq) {
       src[e0] = from_f32<T>(o0);

@@ -10,9 +10,9 @@
 //    exp(-softplus(-z) / tau) in float32; a block takes eight tokens and 256 channels, r ascending.
 //  * gla_scan: the recurrence over this step's tokens of every request row, from the state that the
 //    request's slot holds, which is left updated.  Float32 throughout; q, k, v are read in the
-//    activation type.  One block of 512 threads per (columns of vdim, head, row); a thread keeps four
-//    consecutive key channels of one column of S in registers (up to 32 consecutive lanes share a column; the
-//    state is stored [vdim][dim], so a column's lanes read one contiguous run), the step's
+//    activation type.  One block of 128 threads per (columns of vdim, head, row); a thread keeps four
+//    consecutive key channels of each of four columns of S in registers (up to 32 consecutive lanes share a
+//    column; the state is stored [vdim][dim], so a column's lanes read one contiguous run), the step's
 //    q, k, alpha and v are staged in shared memory a chunk of tokens at a time, and o_t[j] is the sum
 //    over the column's lanes.  The order of every sum depends on (dim, vdim) only: a token's result
 //    does not depend on how the prompt was cut or on what else is in the batch.
@@ -21,7 +21,8 @@
 #include "common.cuh"
 using namespace arle;
 
-constexpr int kScanThreads = 512;
+constexpr int kScanThreads = 128;
+constexpr int kScanCpt = 4;                      // columns of the state a thread keeps
 constexpr int kDecayTokens = 8;                  // tokens a block of the decay kernel takes
 
 // w2t is the second matrix of the gate transposed, [rank][channels]: consecutive threads read consecutive floats.
@@ -67,10 +68,12 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
   return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
 
-// DPT: consecutive key channels of one column of the state that a thread keeps (4 up to 128 channels, then 8, 16).
-// LPC: lanes that share a column (a power of two; LPC * DPT >= dim).  VEC: four channels at a time can be fetched
-// with one aligned load.  A chunk of CHUNK tokens is staged in shared memory; while it is worked on, the next
-// chunk's q, k, alpha and v are already on their way into registers.
+// DPT: consecutive key channels that a thread keeps of each of its kScanCpt columns of the state (4 up to 128
+// channels, then 8, 16).  LPC: lanes that share a column (a power of two; LPC * DPT >= dim).  VEC: four channels
+// at a time can be fetched with one aligned load.  A chunk of CHUNK tokens is staged in shared memory; while it is
+// worked on, the next chunk's q, k, alpha and v are already on their way into registers.  Every number of q, k and
+// alpha that a thread reads from shared memory serves four columns: with one column a thread the kernel was bound by
+// shared-memory bandwidth.
 template <typename T, int DPT, int LPC, bool VEC>
 __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
@@ -78,7 +81,8 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     const int* __restrict__ state_slots, float* __restrict__ out, int heads, int dim, int vdim, float q_scale) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int COLS = kScanThreads / LPC;
+  constexpr int CPT = kScanCpt;
+  constexpr int COLS = kScanThreads / LPC * CPT; // columns a block takes
   constexpr int DSPAN = DPT * LPC;               // dim rounded up; channels past dim hold zeros
   constexpr int PAD = DPT == 4 ? 4 : DPT + 4;    // floats a thread's channels take in shared memory: 16-byte rows, spread over the banks
   constexpr int DPAD = PAD * LPC;
@@ -87,26 +91,30 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
   constexpr int QPT = (QUADS + kScanThreads - 1) / kScanThreads;
   constexpr int VPT = (CHUNK * COLS + kScanThreads - 1) / kScanThreads;
   __shared__ __align__(16) float qs[CHUNK * DPAD], ks[CHUNK * DPAD], as[CHUNK * DPAD];
-  __shared__ float vs[CHUNK * COLS];
+  __shared__ __align__(16) float vs[CHUNK * COLS];
   const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * COLS;
   const int l = threadIdx.x & (LPC - 1), jl = threadIdx.x / LPC;
-  const int j = j0 + jl;
-  const bool col_ok = j < vdim;
+  const int jb = j0 + jl * CPT;                  // this thread's first column
   const int t_begin = q_indptr[r], t_end = q_indptr[r + 1];
-  // the state of a head is kept as [vdim][dim]: a thread's channels of its column are contiguous
-  float* S_g = state + (((size_t)state_slots[r] * heads + h) * vdim + (col_ok ? j : 0)) * dim + l * DPT;
+  // the state of a head is kept as [vdim][dim]: a thread's channels of a column are contiguous
+  float* S_g = state + (((size_t)state_slots[r] * heads + h) * vdim) * dim + l * DPT;
   const bool vec_state = (dim & 3) == 0;
-  float S[DPT];
+  float S[CPT][DPT];
 #pragma unroll
-  for (int i = 0; i < DPT; i += 4) {
-    const int c = l * DPT + i;
-    if (vec_state) {
-      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (col_ok && c < dim) u = *reinterpret_cast<const float4*>(S_g + i);
-      S[i] = u.x, S[i + 1] = u.y, S[i + 2] = u.z, S[i + 3] = u.w;
-    } else {
+  for (int cc = 0; cc < CPT; ++cc) {
+    const bool col_ok = jb + cc < vdim;
+    const float* sp = S_g + (size_t)(col_ok ? jb + cc : 0) * dim;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) S[i + e] = (col_ok && c + e < dim) ? S_g[i + e] : 0.f;
+    for (int i = 0; i < DPT; i += 4) {
+      const int c = l * DPT + i;
+      if (vec_state) {
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (col_ok && c < dim) u = *reinterpret_cast<const float4*>(sp + i);
+        S[cc][i] = u.x, S[cc][i + 1] = u.y, S[cc][i + 2] = u.z, S[cc][i + 3] = u.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[cc][i + e] = (col_ok && c + e < dim) ? sp[i + e] : 0.f;
+      }
     }
   }
   const size_t hq = (size_t)h * dim, hv = (size_t)h * vdim;
@@ -171,38 +179,67 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
 #pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      const float vj = vs[tt * COLS + jl];
+      const float4 v4 = *reinterpret_cast<const float4*>(vs + tt * COLS + jl * CPT);
+      const float vj[CPT] = {v4.x, v4.y, v4.z, v4.w};
       const float4* qt = reinterpret_cast<const float4*>(qs + tt * DPAD + l * PAD);
       const float4* kt = reinterpret_cast<const float4*>(ks + tt * DPAD + l * PAD);
       const float4* at = reinterpret_cast<const float4*>(as + tt * DPAD + l * PAD);
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      float o[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) o[cc] = 0.f;
 #pragma unroll
       for (int i = 0; i < DPT / 4; ++i) {
         const float4 a4 = at[i], k4 = kt[i], q4 = qt[i];
-        S[4 * i] = fmaf(a4.x, S[4 * i], k4.x * vj);
-        S[4 * i + 1] = fmaf(a4.y, S[4 * i + 1], k4.y * vj);
-        S[4 * i + 2] = fmaf(a4.z, S[4 * i + 2], k4.z * vj);
-        S[4 * i + 3] = fmaf(a4.w, S[4 * i + 3], k4.w * vj);
-        acc[0] = fmaf(S[4 * i], q4.x, acc[0]);
-        acc[1] = fmaf(S[4 * i + 1], q4.y, acc[1]);
-        acc[2] = fmaf(S[4 * i + 2], q4.z, acc[2]);
-        acc[3] = fmaf(S[4 * i + 3], q4.w, acc[3]);
-      }
-      float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
-      for (int w = LPC >> 1; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (l == 0 && col_ok) out[(size_t)(t0 + tt) * heads * vdim + hv + j] = o;
+        for (int cc = 0; cc < CPT; ++cc) {
+          S[cc][4 * i] = fmaf(a4.x, S[cc][4 * i], k4.x * vj[cc]);
+          S[cc][4 * i + 1] = fmaf(a4.y, S[cc][4 * i + 1], k4.y * vj[cc]);
+          S[cc][4 * i + 2] = fmaf(a4.z, S[cc][4 * i + 2], k4.z * vj[cc]);
+          S[cc][4 * i + 3] = fmaf(a4.w, S[cc][4 * i + 3], k4.w * vj[cc]);
+          const float lo = fmaf(S[cc][4 * i], q4.x, S[cc][4 * i + 1] * q4.y);
+          const float hi = fmaf(S[cc][4 * i + 2], q4.z, S[cc][4 * i + 3] * q4.w);
+          o[cc] += lo + hi;
+        }
+      }
+      // the four columns' sums over the LPC lanes: two exchanges halve what a lane holds, then a butterfly
+      int mine = 0;                              // the column whose sum this lane ends up with
+      float b;
+      if (LPC >= 4) {
+        const bool up = (l & (LPC / 2)) != 0, up2 = (l & (LPC / 4)) != 0;
+        const float r0 = __shfl_xor_sync(0xffffffffu, up ? o[0] : o[2], LPC / 2);
+        const float r1 = __shfl_xor_sync(0xffffffffu, up ? o[1] : o[3], LPC / 2);
+        const float a0 = (up ? o[2] : o[0]) + r0, a1 = (up ? o[3] : o[1]) + r1;
+        const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? a0 : a1, LPC / 4);
+        b = (up2 ? a1 : a0) + r2;
+        mine = (up ? 2 : 0) + (up2 ? 1 : 0);
+#pragma unroll
+        for (int w = LPC / 8; w > 0; w >>= 1) b += __shfl_xor_sync(0xffffffffu, b, w);
+        if ((l & (LPC / 4 - 1)) == 0 && jb + mine < vdim) out[(size_t)(t0 + tt) * heads * vdim + hv + jb + mine] = b;
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          float x = o[cc];
+#pragma unroll
+          for (int w = LPC >> 1; w > 0; w >>= 1) x += __shfl_xor_sync(0xffffffffu, x, w);
+          if (l == 0 && jb + cc < vdim) out[(size_t)(t0 + tt) * heads * vdim + hv + jb + cc] = x;
+        }
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < DPT; i += 4) {
-    const int c = l * DPT + i;
-    if (vec_state) {
-      if (col_ok && c < dim) *reinterpret_cast<float4*>(S_g + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
-    } else {
+  for (int cc = 0; cc < CPT; ++cc) {
+    const bool col_ok = jb + cc < vdim;
+    float* sp = S_g + (size_t)(col_ok ? jb + cc : 0) * dim;
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (col_ok && c + e < dim) S_g[i + e] = S[i + e];
+    for (int i = 0; i < DPT; i += 4) {
+      const int c = l * DPT + i;
+      if (vec_state) {
+        if (col_ok && c < dim) *reinterpret_cast<float4*>(sp + i) = make_float4(S[cc][i], S[cc][i + 1], S[cc][i + 2], S[cc][i + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (col_ok && c + e < dim) sp[i + e] = S[cc][i + e];
+      }
     }
   }
 }
@@ -258,7 +295,7 @@ namespace {
 template <typename T, int DPT, int LPC>
 int scan_launch(const void* q, const void* k, const void* v, int in_stride, const float* alpha, float* state, const int* q_indptr,
                 const int* state_slots, float* out, int rows, int heads, int dim, int vdim, float q_scale, cudaStream_t s) {
-  constexpr int COLS = kScanThreads / LPC;
+  constexpr int COLS = kScanThreads / LPC * kScanCpt;
   dim3 grid((vdim + COLS - 1) / COLS, heads, rows);
   const size_t eb = sizeof(T) * 4;               // bytes of four elements of q or k
   const bool vec = dim % 4 == 0 && in_stride % 4 == 0 && ((uintptr_t)q % eb) == 0 && ((uintptr_t)k % eb) == 0 &&

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "arle_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "arle_residual_add": [_P, _P, _I, _I, _I, _P],
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
-    "arle_act_mul": [_P, _P, _I, _I, _I, _I, _P],
+    "arle_act_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
     "arle_attention_prep_row": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_head_gate": [_P, _I, _P, _I, _F, _P, _I, _I, _I, _I, _I, _P],
     "arle_weighted_sum": [_P, _F, _P, _F, _P, _I, ctypes.c_longlong, _P],
@@ -773,32 +773,42 @@ ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
     """out[t, i] = act(gate_up[t, 2i]) * gate_up[t, 2i + 1] for ``activation`` "silu" or "gelu_tanh" (the tanh
-    form of gelu); float32 arithmetic, rounded once."""
+    form of gelu); float32 arithmetic, rounded once.  ``out`` may be columns of a wider buffer."""
     T, I = out.shape
     if activation not in ACTIVATIONS:
         raise KernelError(f"act_mul: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
-    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
-        raise KernelError("act_mul: gate_up must be contiguous [T, 2I] and out contiguous [T, I] of one type")
-    _check(library().arle_act_mul(_ptr(gate_up), _ptr(out), _dt(out), T, I, ACTIVATIONS[activation], _stream()), "act_mul")
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or out.stride(1) != 1 or gate_up.dtype != out.dtype:
+        raise KernelError("act_mul: gate_up must be contiguous [T, 2I] and out [T, I] of the same type with unit inner stride")
+    _check(library().arle_act_mul(_ptr(gate_up), _ptr(out), _dt(out), T, I, ACTIVATIONS[activation], out.stride(0) if T > 1 else I,
+                                  _stream()), "act_mul")
 
 
 def gemm_act_mul(x, w: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
-    """The first half of a gated feed-forward with the named activation on the gate: ``gemm_silu_mul`` for any
-    of ``ACTIVATIONS`` (the same fused kernels where the shapes allow them, else the product and the gate kernel)."""
-    if activation == "silu":
-        gemm_silu_mul(x, w, gate_up, out)
-        return
+    """The first half of a gated feed-forward with the named activation on the gate (any of ``ACTIVATIONS``):
+    out[t, i] = act(x[t] . w[2i]) * (x[t] . w[2i + 1]).  ``out`` may be columns of a wider buffer.  Few rows of x
+    take one launch of the weight-streaming kernel (``x`` may then be ``ScaledRows``), many rows one launch of the
+    two-SM tcgen05 kernel, the gate applied to the float32 sums; otherwise the product goes to ``gate_up`` [T, 2I]
+    and the gate kernel follows."""
     if activation not in ACTIVATIONS:
         raise KernelError(f"gemm_act_mul: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    if activation == "silu" and out.is_contiguous():
+        gemm_silu_mul(x, w, gate_up, out)
+        return
     T, I = out.shape
-    if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I):
+    if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I) or out.stride(1) != 1:
         raise KernelError(f"gemm_act_mul: shapes w {tuple(w.shape)} gate_up {tuple(gate_up.shape)} out {tuple(out.shape)}")
-    if (_KERNEL_SET == "fast" and not isinstance(x, ScaledRows) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    code = 1 + ACTIVATIONS[activation]
+    if isinstance(x, ScaledRows):
+        if not (fused_gemm_supported(x.rows, w) and gated_gemm_fits(x.rows.shape[1])):
+            raise KernelError("gemm_act_mul: rows that lack their norm factor need the gated weight-streaming kernel")
+        _fused_gemm(x.rows, w, out, code, x, None)
+        return
+    if (_KERNEL_SET == "fast" and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and fused_gemm_supported(x, w) and skinny_gemm_supported(x, w, out) and gated_gemm_fits(x.shape[1])):
-        _fused_gemm(x, w, out, 1 + ACTIVATIONS[activation], None, None)
+        _fused_gemm(x, w, out, code, None, None)
         return
     if (_KERNEL_SET == "fast" and T >= _GATED_TCGEN05_MIN_ROWS and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-            and tcgen05_gemm_supported(x, w, out)):
+            and tcgen05_gemm_supported(x, w, out) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
         gemm_tcgen05_pair(x, w, out, gated=True, activation=activation)
         return
     gemm(x, w, gate_up)

@@ -122,7 +122,7 @@ class Attention(Mixer):
         return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
     def takes_scaled_rows(self, num_rows):
-        return self.plain_form and ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
+        return ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
 
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_o)
@@ -130,8 +130,8 @@ class Attention(Mixer):
     def _angles(self, qkv, ctx, inv_freq, rdim, general=False):
         """Cosines and sines of the step's positions, evaluated once for all layers that rotate by the same
         frequencies (kept in the step's memo under the encoding's description).  The general preparation takes the
-        table for any head size, from 32 tokens on."""
-        if not rdim or not (qkv.shape[0] >= 32 if general else ops.attention_prep_takes_angles(qkv, self.spec.head_dim, rdim)):
+        table for any head size and any number of tokens."""
+        if not rdim or not (general or ops.attention_prep_takes_angles(qkv, self.spec.head_dim, rdim)):
             return None
         key = ("rotary_angles", getattr(self.position, "spec", None) or id(self.position))
         angles = ctx.memo.get(key)

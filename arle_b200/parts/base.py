@@ -177,6 +177,17 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
+    # Optional, as for mixers: a feed-forward that can stop before its last product lets a block that adds its
+    # branches run ONE output product for all of them (``parts.parallel.ParallelBlock``).
+    def pre_output_width(self) -> Optional[int]:
+        return None
+
+    def output_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_pre(self, x: torch.Tensor, ctx, into: torch.Tensor) -> None:
+        raise NotImplementedError
+
 
 class Block(Part):
     """Arrangement of norms, mixer and feed-forward around the residual stream."""

@@ -102,6 +102,9 @@ class GatedLinearAttention(Mixer):
         s = self.spec
         return StateNeed((s.num_heads, s.value_dim, s.key_dim), torch.float32)     # a head's S, transposed
 
+    def takes_scaled_rows(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_in)
+
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_o)
 

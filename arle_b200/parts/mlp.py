@@ -55,11 +55,22 @@ class GatedMlp(FeedForward):
         return 3 * self.spec.intermediate_size + self.spec.hidden_size
 
     def takes_scaled_rows(self, num_rows):
-        # the gate inside the weight-streaming product is silu
-        return self.spec.activation == "silu" and ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
+        return ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
 
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_down)
+
+    # the feed-forward up to its last product
+    def pre_output_width(self):
+        return self.spec.intermediate_size
+
+    def output_weight(self):
+        return self.w_down
+
+    def forward_pre(self, x, ctx, into):
+        s = self.spec
+        gu = ctx.ws.get("gate_up", (x.shape[0], 2 * s.intermediate_size), x.dtype)
+        ops.gemm_act_mul(x, self.w_gate_up, gu, into, s.activation)
 
     def forward(self, x, ctx, sink=None):
         s = self.spec

@@ -4,12 +4,16 @@
 weights, y = sum_i scale_i * mixer_i(x).  When every member can stop before its output
 projection (``Mixer.pre_output_width``), each writes scale_i times that projection's input
 into its columns of one buffer and ONE product with the members' output matrices side by side
-gives y; otherwise every member runs whole and the outputs are summed by a kernel.  At most one
-member may keep a paged cache and at most one a state per request (the model hands a schedule
-entry one of each).
+gives y (the mixer then offers the same protocol itself); otherwise every member runs whole and
+the outputs are summed by a kernel.  At most one member may keep a paged cache and at most one a
+state per request (the model hands a schedule entry one of each).
 
 ``ParallelBlock``: x <- x + (mixer(n) + ff(n)) with n = norm(x): one norm, both branches read its
-output; the feed-forward may be absent.
+output; the feed-forward may be absent.  When mixer and feed-forward can both stop before their
+last product, the block runs ONE output product over [mixer's columns | feed-forward's columns];
+in a decode step of few rows that product adds into the residual itself and leaves the next
+block's norm behind (``ops.ResidualSink``), and the next block's first products apply the norm's
+factor (``ops.ScaledRows``): no norm kernel and no residual kernel between the blocks.
 """
 from __future__ import annotations
 
@@ -21,6 +25,21 @@ import torch
 from .. import ops
 from .base import Block, Mixer
 from .registry import build_part, register_part
+
+
+def _side_by_side(weights, widths):
+    """The matrices [hidden, width_i] side by side, every one starting on a column that is a multiple of 8
+    (16 bytes in bfloat16).  Returns (matrix, start columns)."""
+    mats, at, col = [], [], 0
+    for wo, w in zip(weights, widths):
+        at.append(col)
+        mats.append(wo)
+        pad = -w % 8
+        if pad:
+            mats.append(torch.zeros((wo.shape[0], pad), dtype=wo.dtype, device=wo.device))
+        col += w + pad
+    wt = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+    return torch.cat([m.to(wt) for m in mats], dim=1).contiguous(), at
 
 
 @dataclass(frozen=True)
@@ -45,6 +64,8 @@ class ParallelMixer(Mixer):
         self.shared_output = all(w is not None for w in widths)
         self.widths = widths if self.shared_output else None
         self.w_o = None
+        self.at = None
+        self.padded = False
 
     def weight_decls(self):
         return tuple(d for m in self.members for d in m.weight_decls())
@@ -53,18 +74,7 @@ class ParallelMixer(Mixer):
         for m in self.members:
             m.load(tensors, dtype, device)
         if self.shared_output:
-            # the members' output matrices side by side; columns padded so that every member's start on 16 bytes
-            mats, self.at, col = [], [], 0
-            for m, w in zip(self.members, self.widths):
-                wo = m.output_weight()
-                self.at.append(col)
-                mats.append(wo)
-                pad = -w % 8
-                if pad:
-                    mats.append(torch.zeros((wo.shape[0], pad), dtype=wo.dtype, device=wo.device))
-                col += w + pad
-            wt = torch.float32 if any(m_.dtype == torch.float32 for m_ in mats) else mats[0].dtype
-            self.w_o = torch.cat([m_.to(wt) for m_ in mats], dim=1).contiguous()
+            self.w_o, self.at = _side_by_side([m.output_weight() for m in self.members], self.widths)
             self.padded = any(-w % 8 for w in self.widths)
 
     def weight_bytes(self):
@@ -79,22 +89,36 @@ class ParallelMixer(Mixer):
     def state_need(self):
         return self.members[self.with_state[0]].state_need() if self.with_state else None
 
+    def takes_scaled_rows(self, num_rows):
+        return self.shared_output and all(m.takes_scaled_rows(num_rows) for m in self.members)
+
     def can_sink(self, num_rows):
         return self.shared_output and ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
     def _args(self, i, cache, state):
         return (cache if i in self.with_cache else None, state if i in self.with_state else None)
 
+    # the mixer up to its one output product
+    def pre_output_width(self):
+        return self.w_o.shape[1] if self.shared_output and self.w_o is not None else (
+            sum(w + -w % 8 for w in self.widths) if self.shared_output else None)
+
+    def output_weight(self):
+        return self.w_o
+
+    def forward_pre(self, x, ctx, cache, state, into, scale):
+        if self.padded:
+            into.zero_()
+        for i, (m, w) in enumerate(zip(self.members, self.widths)):
+            c, st = self._args(i, cache, state)
+            m.forward_pre(x, ctx, c, st, into[:, self.at[i]: self.at[i] + w], scale * self.spec.scales[i])
+
     def forward(self, x, ctx, cache, state, sink=None):
         T = x.shape[0]
         H = self.spec.hidden_size
         if self.shared_output:
             cat = ctx.ws.get("parallel_pre", (T, self.w_o.shape[1]), x.dtype)
-            if self.padded:
-                cat.zero_()
-            for i, (m, w) in enumerate(zip(self.members, self.widths)):
-                c, st = self._args(i, cache, state)
-                m.forward_pre(x, ctx, c, st, cat[:, self.at[i]: self.at[i] + w], self.spec.scales[i])
+            self.forward_pre(x, ctx, cache, state, cat, 1.0)
             out = ctx.ws.get("mixer_out", (T, H), x.dtype)
             return None if ops.gemm(cat, self.w_o, out, sink=sink) else out
         total = None
@@ -125,6 +149,10 @@ class ParallelBlock(Block):
         self.mixer = build_part(spec.mixer)
         self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
         self._parts = tuple(p for p in (self.norm, self.mixer, self.ffn) if p is not None)
+        self.one_product = self.mixer.pre_output_width() is not None and (self.ffn is None or self.ffn.pre_output_width() is not None)
+        self.w_out = None
+        self.at = None
+        self.padded = False
 
     def weight_decls(self):
         return tuple(d for p in self._parts for d in p.weight_decls())
@@ -132,18 +160,48 @@ class ParallelBlock(Block):
     def load(self, tensors, dtype, device):
         for p in self._parts:
             p.load(tensors, dtype, device)
+        if self.one_product:
+            branches = [self.mixer] + ([self.ffn] if self.ffn is not None else [])
+            widths = [b.pre_output_width() for b in branches]
+            self.w_out, self.at = _side_by_side([b.output_weight() for b in branches], widths)
+            self.widths = widths
+            self.padded = any(-w % 8 for w in widths)
 
     def weight_bytes(self):
         return sum(p.weight_bytes() for p in self._parts)
 
     def scratch_elements_per_token(self):
-        return sum(p.scratch_elements_per_token() for p in self._parts)
+        return sum(p.scratch_elements_per_token() for p in self._parts) + (self.w_out.shape[1] if self.w_out is not None else 0)
+
+    def entry(self):
+        return self.norm, self
+
+    def takes_scaled_rows(self, num_rows):
+        """Asked by the block before this one: can every first product of this block apply the norm's factor itself?"""
+        return (self.one_product and self.mixer.takes_scaled_rows(num_rows)
+                and (self.ffn is None or self.ffn.takes_scaled_rows(num_rows)))
 
     def forward(self, stream, ctx, cache, state):
         n = stream.normed(self.norm, "normed_a")
-        stream.add(self.mixer.forward(n, ctx, cache, state))
+        if not self.one_product:
+            stream.add(self.mixer.forward(n, ctx, cache, state))
+            if self.ffn is not None:
+                stream.add(self.ffn.forward(n, ctx))
+            return
+        T = ctx.num_tokens
+        pre = ctx.ws.get("block_pre", (T, self.w_out.shape[1]), n.dtype)
+        if self.padded:
+            pre.zero_()
+        self.mixer.forward_pre(n, ctx, cache, state, pre[:, : self.widths[0]], 1.0)
         if self.ffn is not None:
-            stream.add(self.ffn.forward(n, ctx))
+            self.ffn.forward_pre(n, ctx, pre[:, self.at[1]: self.at[1] + self.widths[1]])
+        nxt = stream.next_entry
+        sink = None
+        if nxt is not None and ops.fused_gemm_shape_ok(T, self.w_out):
+            # every reader of this block's normed rows has run by now: their buffer can take the next block's
+            sink = stream.sink_for(nxt[0], nxt[1], "normed_a")
+        out = ctx.ws.get("block_out", (T, stream.resid.shape[1]), n.dtype)
+        stream.add(None if ops.gemm(pre, self.w_out, out, sink=sink) else out)
 
 
 register_part(ParallelMixerSpec.kind, ParallelMixer)

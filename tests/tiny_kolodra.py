@@ -32,9 +32,18 @@ TINY_K2 = {"architecture": "Kolodra", "vocab": 301, "width": 96, "embedding": {"
 _K3 = (4, 1, 64, 64, 50000.0, 0.125, 2, 128, 64, 16.0, 16, 1.1, 0.8, 512)
 TINY_K3 = {"architecture": "Kolodra", "vocab": 512, "width": 256, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6},
            "logit_softcap": 20.0, "layers": [_layer(*_K3), _layer(*_K3), _layer(*_K3, weights_of=0)]}
-CONFIGS = {"K1": TINY_K1, "K2": TINY_K2, "K3": TINY_K3}
-INIT = {"K1": dict(sigma=0.12, gain_jitter=0.2), "K2": dict(sigma=0.1, gain_jitter=0.3), "K3": dict(sigma=0.06, gain_jitter=0.2)}
-PAGE_SIZES = {"K1": 4, "K2": 8, "K3": 16}
+# K4: sizes that are multiples of nothing useful (width 100, head 36, odd vocabulary): every kernel's general path
+_K4 = (2, 1, 36, 12, 777.0, 0.21, 3, 20, 12, 3.0, 2, 0.9, 1.1, 52)
+TINY_K4 = {"architecture": "Kolodra", "vocab": 257, "width": 100, "embedding": {"scale": 2.5}, "norm": {"eps": 2e-6},
+           "logit_softcap": 7.5, "layers": [_layer(*_K4), _layer(*_K4, weights_of=0), _layer(*_K4)]}
+# K5: head size 128 on the softmax side (the tcgen05 prefill attention in bfloat16), a chain of shared layers
+_K5 = (2, 2, 128, 128, 200000.0, 0.08838834764831845, 2, 64, 32, 32.0, 8, 1.0, 1.25, 256)
+TINY_K5 = {"architecture": "Kolodra", "vocab": 640, "width": 128, "embedding": {"scale": 11.0}, "norm": {"eps": 1e-5},
+           "logit_softcap": 25.0, "layers": [_layer(*_K5), _layer(*_K5, weights_of=0), _layer(*_K5, weights_of=1)]}
+CONFIGS = {"K1": TINY_K1, "K2": TINY_K2, "K3": TINY_K3, "K4": TINY_K4, "K5": TINY_K5}
+INIT = {"K1": dict(sigma=0.12, gain_jitter=0.2), "K2": dict(sigma=0.1, gain_jitter=0.3), "K3": dict(sigma=0.06, gain_jitter=0.2),
+        "K4": dict(sigma=0.1, gain_jitter=0.2), "K5": dict(sigma=0.08, gain_jitter=0.2)}
+PAGE_SIZES = {"K1": 4, "K2": 8, "K3": 16, "K4": 16, "K5": 16}
 
 
 def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
