@@ -61,12 +61,17 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ lo
   }
 }
 
-__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
-  const uint2 u = *reinterpret_cast<const uint2*>(p);
+// Four elements as they lie in memory (converted only when they are staged: a conversion right after its load would
+// make every load wait for the one before it).
+__device__ __forceinline__ float4 load_raw4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ uint2 load_raw4(const __nv_bfloat16* p) { return *reinterpret_cast<const uint2*>(p); }
+__device__ __forceinline__ float4 widen4(float4 u) { return u; }
+__device__ __forceinline__ float4 widen4(uint2 u) {
   const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
   return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
+template <typename T, bool VEC> struct Raw4 { using type = float4; };
+template <> struct Raw4<__nv_bfloat16, true> { using type = uint2; };
 
 // DPT: consecutive key channels that a thread keeps of each of its kScanCpt columns of the state (4 up to 128
 // channels, then 8, 16).  LPC: lanes that share a column (a power of two; LPC * DPT >= dim).  VEC: four channels
@@ -119,62 +124,75 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
   }
   const size_t hq = (size_t)h * dim, hv = (size_t)h * vdim;
   const size_t a_stride = (size_t)heads * dim;
-  float4 rq[QPT], rk[QPT], ra[QPT];
-  float rv[VPT];
+  using RawT = typename Raw4<T, VEC>::type;
+  RawT rq[QPT], rk[QPT];
+  float4 ra[QPT];
+  T rv[VPT];
 
-  auto fetch = [&](int t0, int n) {              // the chunk's numbers into registers; nothing waits on them yet
+  // The chunk's numbers into registers; nothing waits on them yet.  Loads are unconditional (a place outside the
+  // chunk reads the row's first token instead and is zeroed when staged), so that they are all under way at once.
+  auto fetch = [&](int t0, int n) {
 #pragma unroll
     for (int u = 0; u < QPT; ++u) {
       const int idx = threadIdx.x + u * kScanThreads;
       const int tt = idx / (DSPAN / 4), c = (idx - tt * (DSPAN / 4)) * 4;
-      float4 fq = make_float4(0.f, 0.f, 0.f, 0.f), fk = fq, fa = fq;
-      if (idx < QUADS && tt < n && c < dim) {
-        const size_t row = (size_t)(t0 + tt);
-        if (VEC) {
-          fq = load4(q + row * in_stride + hq + c);
-          fk = load4(k + row * in_stride + hq + c);
-          fa = load4(alpha + row * a_stride + hq + c);
-        } else {
-          float* pq = &fq.x; float* pk = &fk.x; float* pa = &fa.x;
+      const bool ok = idx < QUADS && tt < n && c < dim;
+      const size_t row = ok ? (size_t)(t0 + tt) : (size_t)t_begin;
+      const int cs = ok ? c : 0;
+      if constexpr (VEC) {
+        rq[u] = load_raw4(q + row * in_stride + hq + cs);
+        rk[u] = load_raw4(k + row * in_stride + hq + cs);
+        ra[u] = *reinterpret_cast<const float4*>(alpha + row * a_stride + hq + cs);
+      } else {
+        float4 fq = make_float4(0.f, 0.f, 0.f, 0.f), fk = fq, fa = fq;
+        float* pq = &fq.x; float* pk = &fk.x; float* pa = &fa.x;
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (c + e < dim) {
-              pq[e] = to_f32(q[row * in_stride + hq + c + e]);
-              pk[e] = to_f32(k[row * in_stride + hq + c + e]);
-              pa[e] = alpha[row * a_stride + hq + c + e];
-            }
-        }
+        for (int e = 0; e < 4; ++e)
+          if (cs + e < dim) {
+            pq[e] = to_f32(q[row * in_stride + hq + cs + e]);
+            pk[e] = to_f32(k[row * in_stride + hq + cs + e]);
+            pa[e] = alpha[row * a_stride + hq + cs + e];
+          }
+        *reinterpret_cast<float4*>(&rq[u]) = fq;
+        *reinterpret_cast<float4*>(&rk[u]) = fk;
+        ra[u] = fa;
       }
-      rq[u] = fq, rk[u] = fk, ra[u] = fa;
     }
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
       const int idx = threadIdx.x + u * kScanThreads;
       const int tt = idx / COLS, c = idx - tt * COLS;
-      rv[u] = (idx < CHUNK * COLS && tt < n && j0 + c < vdim) ? to_f32(v[(size_t)(t0 + tt) * in_stride + hv + j0 + c]) : 0.f;
+      const bool ok = idx < CHUNK * COLS && tt < n && j0 + c < vdim;
+      rv[u] = v[(ok ? (size_t)(t0 + tt) : (size_t)t_begin) * in_stride + hv + (ok ? j0 + c : 0)];
     }
   };
-  auto stage = [&]() {                           // registers to shared memory, q scaled on the way
+  auto stage = [&](int n) {                      // registers to shared memory, widened, q scaled on the way
 #pragma unroll
     for (int u = 0; u < QPT; ++u) {
       const int idx = threadIdx.x + u * kScanThreads;
       const int tt = idx / (DSPAN / 4), c = (idx - tt * (DSPAN / 4)) * 4;
       const int at = tt * DPAD + (c / DPT) * PAD + (c % DPT);
       if (idx >= QUADS) continue;
-      *reinterpret_cast<float4*>(qs + at) = make_float4(rq[u].x * q_scale, rq[u].y * q_scale, rq[u].z * q_scale, rq[u].w * q_scale);
-      *reinterpret_cast<float4*>(ks + at) = rk[u];
-      *reinterpret_cast<float4*>(as + at) = ra[u];
+      const bool ok = tt < n && c < dim;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 fq = widen4(rq[u]), fk = widen4(rk[u]);
+      *reinterpret_cast<float4*>(qs + at) = ok ? make_float4(fq.x * q_scale, fq.y * q_scale, fq.z * q_scale, fq.w * q_scale) : z;
+      *reinterpret_cast<float4*>(ks + at) = ok ? fk : z;
+      *reinterpret_cast<float4*>(as + at) = ok ? ra[u] : z;
     }
 #pragma unroll
-    for (int u = 0; u < VPT; ++u)
-      if (threadIdx.x + u * kScanThreads < CHUNK * COLS) vs[threadIdx.x + u * kScanThreads] = rv[u];
+    for (int u = 0; u < VPT; ++u) {
+      const int idx = threadIdx.x + u * kScanThreads;
+      const int tt = idx / COLS, c = idx - tt * COLS;
+      if (idx < CHUNK * COLS) vs[idx] = (tt < n && j0 + c < vdim) ? to_f32(rv[u]) : 0.f;
+    }
   };
 
   if (t_begin < t_end) fetch(t_begin, min(CHUNK, t_end - t_begin));
   for (int t0 = t_begin; t0 < t_end; t0 += CHUNK) {
     const int n = min(CHUNK, t_end - t0);
     __syncthreads();                             // the chunk before has been read by everyone
-    stage();
+    stage(n);
     __syncthreads();
     if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
 #pragma unroll 2
