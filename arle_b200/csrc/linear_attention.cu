@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
     stage(n);
     __syncthreads();
     if (t0 + CHUNK < t_end) fetch(t0 + CHUNK, min(CHUNK, t_end - t0 - CHUNK));
-#pragma unroll 2
+#pragma unroll 4
     for (int tt = 0; tt < n; ++tt) {
       const float4 v4 = *reinterpret_cast<const float4*>(vs + tt * COLS + jl * CPT);
       const float vj[CPT] = {v4.x, v4.y, v4.z, v4.w};

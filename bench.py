@@ -182,6 +182,8 @@ def design_table(args, torch, ops, pk) -> int:
                     head_dim=z["hd"], intermediate_size=z["ff"], vocab_size=z["vocab"])
 
     def timeline(fn):
+        if args.no_kernel_times:
+            return {}
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             fn()
             torch.cuda.synchronize()
@@ -285,6 +287,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: tokens each request holds")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: tokens of the prompt")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--no-kernel-times", action="store_true",
+                    help="with --design: leave out the per-kernel times (they come from torch's profiler, which cannot run under another profiler)")
     ap.add_argument("--design", default=None, choices=["kolodra"],
                     help="instead of the default workload: a few layers of this design beside as many Qwen3 layers of equal "
                          "sizes, prefill and decode, with every kernel's time (uses --layers, --steps, --context, --prefill-tokens)")
