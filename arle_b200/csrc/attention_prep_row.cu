@@ -24,7 +24,7 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
                                           const float* __restrict__ k_weight, float eps,
                                           const float* __restrict__ inv_freq, const float2* __restrict__ angles,
                                           int rotary_dim, int pairing, int values_are_keys, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                          int nq, int nkv, int hd, int page_size) {
+                                          int nq, int nkv, int hd, int page_size, int vec8) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float row[];                 // (nq + nkv) * hd floats: x * weight, still without the row's factor
@@ -36,12 +36,30 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
   const int slot = nkv > 0 ? slot_mapping[t] : -1;
   const float pos = (float)positions[t];
   float sq = 0.f, sk = 0.f;
-  for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
-    const float x = to_f32(src[e]);
-    const float* wt = e < nqe ? q_weight : k_weight;
-    const float w = wt ? wt[e < nqe ? e : e - nqe] : 1.0f;
-    row[e] = x * w;
-    if (e < nqe) sq += x * x; else sk += x * x;
+  if (sizeof(T) == 2 && vec8) {                  // bfloat16 rows on 16-byte boundaries, q's and k's widths multiples of 8
+    for (int e = threadIdx.x * 8; e < nqe + nke; e += blockDim.x * 8) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + e);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+      const float* wt = e < nqe ? q_weight : k_weight;
+      const float* wp = wt ? wt + (e < nqe ? e : e - nqe) : nullptr;
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = __low2float(h2[i]), b = __high2float(h2[i]);
+        row[e + 2 * i] = wp ? a * wp[2 * i] : a;
+        row[e + 2 * i + 1] = wp ? b * wp[2 * i + 1] : b;
+        s += a * a + b * b;
+      }
+      if (e < nqe) sq += s; else sk += s;
+    }
+  } else {
+    for (int e = threadIdx.x; e < nqe + nke; e += blockDim.x) {
+      const float x = to_f32(src[e]);
+      const float* wt = e < nqe ? q_weight : k_weight;
+      const float w = wt ? wt[e < nqe ? e : e - nqe] : 1.0f;
+      row[e] = x * w;
+      if (e < nqe) sq += x * x; else sk += x * x;
+    }
   }
   {                                              // both sums in one pass over the block
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
@@ -87,15 +105,26 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
       e1 = e0 + 1;
       o0 = row[e0] * inv, o1 = row[e1] * inv;
     }
+    const bool pair = sizeof(T) == 2 && vec8 && e1 == e0 + 1;      // neighbours: one 4-byte access for both
     if (head < nq) {
-      src[e0] = from_f32<T>(o0);
-      src[e1] = from_f32<T>(o1);
+      if (pair) {
+        *reinterpret_cast<__nv_bfloat162*>(src + e0) = __floats2bfloat162_rn(o0, o1);
+      } else {
+        src[e0] = from_f32<T>(o0);
+        src[e1] = from_f32<T>(o1);
+      }
     } else if (slot >= 0) {
       const size_t base = (((size_t)page * nkv + (head - nq)) * page_size + off) * hd - (size_t)head * hd;
-      k_cache[base + e0] = from_f32<T>(o0);
-      k_cache[base + e1] = from_f32<T>(o1);
-      v_cache[base + e0] = values_are_keys ? src[e0] : src[e0 + nke];
-      v_cache[base + e1] = values_are_keys ? src[e1] : src[e1 + nke];
+      const T* vsrc = values_are_keys ? src : src + nke;
+      if (pair) {
+        *reinterpret_cast<__nv_bfloat162*>(k_cache + base + e0) = __floats2bfloat162_rn(o0, o1);
+        *reinterpret_cast<uint32_t*>(v_cache + base + e0) = *reinterpret_cast<const uint32_t*>(vsrc + e0);
+      } else {
+        k_cache[base + e0] = from_f32<T>(o0);
+        k_cache[base + e1] = from_f32<T>(o1);
+        v_cache[base + e0] = vsrc[e0];
+        v_cache[base + e1] = vsrc[e1];
+      }
     }
   }
 }
@@ -113,19 +142,23 @@ ARLE_API int arle_attention_prep_row(void* qk, int dtype, int row_stride, const 
   const size_t smem = (size_t)(nq + nkv) * hd * sizeof(float);
   if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
   const int n = (nq + nkv) * hd;
-  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  const int threads = n >= 4096 ? 512 : (n >= 512 ? 256 : 128);
+  // wide accesses: every row, head and cache entry starts on a 16-byte boundary (even head sizes keep pairs on 4)
+  const int vec8 = dtype == 1 && (nq * hd) % 8 == 0 && (nkv * hd) % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)qk % 16) == 0 &&
+                   ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)q_weight % 16) == 0 &&
+                   ((uintptr_t)k_weight % 16) == 0;
   if (dtype == 0) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(attention_prep_row_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(attention_prep_row_kernel<float>, dim3(num_tokens), dim3(threads), smem, s, 1, (float*)qk, row_stride, positions,
                   slot_mapping, q_weight, k_weight, eps, inv_freq, (const float2*)angles, rotary_dim, pairing, values_are_keys, (float*)k_cache,
-                  (float*)v_cache, nq, nkv, hd, page_size);
+                  (float*)v_cache, nq, nkv, hd, page_size, vec8);
   } else if (dtype == 1) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(attention_prep_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(attention_prep_row_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), smem, s, 1, (__nv_bfloat16*)qk,
                   row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, (const float2*)angles, rotary_dim, pairing,
                   values_are_keys,
-                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, hd, page_size);
+                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, hd, page_size, vec8);
   } else {
     return ARLE_E_BADARG;
   }

@@ -7,7 +7,7 @@
 //
 //  * gla_decay: alpha[t, c] = sigmoid(z)^(1/tau), z = b[c] + sum_r low[t, r] * w2[c, r], the second
 //    half of a low-rank gate (low = W_a1 x comes from the packed input projection).  Evaluated as
-//    exp(-softplus(-z) / tau) in float32; a block takes eight tokens and 256 channels, r ascending.
+//    exp(-softplus(-z) / tau) in float32; a block takes sixteen tokens and 256 channels, r ascending.
 //  * gla_scan: the recurrence over this step's tokens of every request row, from the state that the
 //    request's slot holds, which is left updated.  Float32 throughout; q, k, v are read in the
 //    activation type.  One block of 128 threads per (columns of vdim, head, row); a thread keeps four
@@ -23,7 +23,8 @@ using namespace arle;
 
 constexpr int kScanThreads = 128;
 constexpr int kScanCpt = 4;                      // columns of the state a thread keeps
-constexpr int kDecayTokens = 8;                  // tokens a block of the decay kernel takes
+constexpr int kDecayTokens = 16;                 // tokens a block of the decay kernel takes
+constexpr int kDecayBatch = 16;                  // weights a thread asks for before it uses the first
 
 // w2t is the second matrix of the gate transposed, [rank][channels]: consecutive threads read consecutive floats.
 template <typename T>
@@ -45,11 +46,16 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ lo
   float z[kDecayTokens];
 #pragma unroll
   for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = 0.f;
-#pragma unroll 8
-  for (int r = 0; r < rank; ++r) {
-    const float w = w2t[(size_t)r * channels + c];
+  for (int r0 = 0; r0 < rank; r0 += kDecayBatch) {
+    float w[kDecayBatch];
 #pragma unroll
-    for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(lo_s[tt * rank + r], w, z[tt]);
+    for (int i = 0; i < kDecayBatch; ++i) w[i] = r0 + i < rank ? w2t[(size_t)(r0 + i) * channels + c] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kDecayBatch; ++i) {
+      if (r0 + i >= rank) break;
+#pragma unroll
+      for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(lo_s[tt * rank + r0 + i], w[i], z[tt]);
+    }
   }
   const float b = bias ? bias[c] : 0.f;
 #pragma unroll
@@ -262,7 +268,15 @@ __global__ void __launch_bounds__(kScanThreads) gla_scan_kernel(
   }
 }
 
-template <typename T>
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+template <typename T, bool VEC4>
 __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
                                const float* __restrict__ weight, float eps, float scale, T* __restrict__ out,
                                int out_stride, int heads, int vdim, long long units) {
@@ -275,17 +289,42 @@ __global__ void gla_out_kernel(const float* __restrict__ o, const T* __restrict_
   const int h = (int)(unit - t * heads);
   const float* src = o + ((size_t)t * heads + h) * vdim;
   float ss = 0.f;
-  for (int e = lane; e < vdim; e += 32) ss += src[e] * src[e];
-  ss = warp_sum(ss);
-  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
-  for (int e = lane; e < vdim; e += 32) {
-    float y = src[e] * inv;
-    if (weight) y *= weight[e];
-    if (gate) {
-      const float g = to_f32(gate[(size_t)t * gate_stride + (size_t)h * vdim + e]);
-      y *= g / (1.0f + expf(-g));
+  if constexpr (VEC4) {                          // vdim a multiple of 4, rows on 16-byte (8-byte for bfloat16) boundaries
+    const T* gp = gate ? gate + (size_t)t * gate_stride + (size_t)h * vdim : nullptr;
+    T* op = out + (size_t)t * out_stride + (size_t)h * vdim;
+    for (int e = lane * 4; e < vdim; e += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(src + e);
+      ss += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
     }
-    out[(size_t)t * out_stride + (size_t)h * vdim + e] = from_f32<T>(y * scale);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int e = lane * 4; e < vdim; e += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(src + e);
+      float y[4] = {x.x * inv, x.y * inv, x.z * inv, x.w * inv};
+      if (weight) {
+        const float4 w = *reinterpret_cast<const float4*>(weight + e);
+        y[0] *= w.x, y[1] *= w.y, y[2] *= w.z, y[3] *= w.w;
+      }
+      if (gp) {
+        const float4 g = widen4(load_raw4(gp + e));
+        y[0] *= g.x / (1.0f + expf(-g.x)), y[1] *= g.y / (1.0f + expf(-g.y));
+        y[2] *= g.z / (1.0f + expf(-g.z)), y[3] *= g.w / (1.0f + expf(-g.w));
+      }
+      store4(op + e, y[0] * scale, y[1] * scale, y[2] * scale, y[3] * scale);
+    }
+  } else {
+    for (int e = lane; e < vdim; e += 32) ss += src[e] * src[e];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int e = lane; e < vdim; e += 32) {
+      float y = src[e] * inv;
+      if (weight) y *= weight[e];
+      if (gate) {
+        const float g = to_f32(gate[(size_t)t * gate_stride + (size_t)h * vdim + e]);
+        y *= g / (1.0f + expf(-g));
+      }
+      out[(size_t)t * out_stride + (size_t)h * vdim + e] = from_f32<T>(y * scale);
+    }
   }
 }
 
@@ -370,13 +409,19 @@ ARLE_API int arle_gla_out(const float* o, const void* gate, int dtype, int gate_
   const int warps = 8;
   const long long blocks = (units + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return ARLE_E_UNSUPPORTED;
-  if (dtype == 0)
-    launch_kernel(gla_out_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const float*)gate, gate_stride, weight,
-                  eps, scale, (float*)out, out_stride, heads, vdim, units);
-  else if (dtype == 1)
-    launch_kernel(gla_out_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const __nv_bfloat16*)gate,
-                  gate_stride, weight, eps, scale, (__nv_bfloat16*)out, out_stride, heads, vdim, units);
-  else
+  const size_t eb = dtype == 0 ? 16 : 8;         // bytes of four elements of gate and out
+  const bool vec = vdim % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && ((uintptr_t)o % 16) == 0 &&
+                   ((uintptr_t)gate % eb) == 0 && ((uintptr_t)out % eb) == 0 && ((uintptr_t)weight % 16) == 0;
+  if (dtype == 0) {
+    auto kern = vec ? gla_out_kernel<float, true> : gla_out_kernel<float, false>;
+    launch_kernel(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const float*)gate, gate_stride, weight, eps, scale,
+                  (float*)out, out_stride, heads, vdim, units);
+  } else if (dtype == 1) {
+    auto kern = vec ? gla_out_kernel<__nv_bfloat16, true> : gla_out_kernel<__nv_bfloat16, false>;
+    launch_kernel(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, s, 1, o, (const __nv_bfloat16*)gate, gate_stride, weight, eps,
+                  scale, (__nv_bfloat16*)out, out_stride, heads, vdim, units);
+  } else {
     return ARLE_E_BADARG;
+  }
   return launch_status();
 }
