@@ -27,7 +27,7 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
                                           int nq, int nkv, int hd, int page_size, int vec8) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float row[];                 // (nq + nkv) * hd floats: x * weight, still without the row's factor
+  extern __shared__ __align__(16) float row[];                 // (nq + nkv) * hd floats: x * weight, still without the row's factor
   __shared__ float red[2][33];
   const int t = blockIdx.x;
   const int nqe = nq * hd, nke = nkv * hd;
@@ -42,14 +42,19 @@ __global__ void attention_prep_row_kernel(T* __restrict__ qk, int row_stride, co
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
       const float* wt = e < nqe ? q_weight : k_weight;
       const float* wp = wt ? wt + (e < nqe ? e : e - nqe) : nullptr;
-      float s = 0.f;
+      float s = 0.f, xw[8];
+      float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+      if (wp) w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float a = __low2float(h2[i]), b = __high2float(h2[i]);
-        row[e + 2 * i] = wp ? a * wp[2 * i] : a;
-        row[e + 2 * i + 1] = wp ? b * wp[2 * i + 1] : b;
+        xw[2 * i] = a * wv[2 * i];
+        xw[2 * i + 1] = b * wv[2 * i + 1];
         s += a * a + b * b;
       }
+      *reinterpret_cast<float4*>(row + e) = make_float4(xw[0], xw[1], xw[2], xw[3]);
+      *reinterpret_cast<float4*>(row + e + 4) = make_float4(xw[4], xw[5], xw[6], xw[7]);
       if (e < nqe) sq += s; else sk += s;
     }
   } else {
@@ -142,7 +147,7 @@ ARLE_API int arle_attention_prep_row(void* qk, int dtype, int row_stride, const 
   const size_t smem = (size_t)(nq + nkv) * hd * sizeof(float);
   if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
   const int n = (nq + nkv) * hd;
-  const int threads = n >= 4096 ? 512 : (n >= 512 ? 256 : 128);
+  const int threads = n >= 512 ? 256 : 128;
   // wide accesses: every row, head and cache entry starts on a 16-byte boundary (even head sizes keep pairs on 4)
   const int vec8 = dtype == 1 && (nq * hd) % 8 == 0 && (nkv * hd) % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)qk % 16) == 0 &&
                    ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)q_weight % 16) == 0 &&
