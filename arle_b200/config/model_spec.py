@@ -39,6 +39,7 @@ class ModelSpec:
     kind: str = "decoder"                     # the registered model class that is built from this spec
     embed_scale: float = 1.0                  # the embedding row is multiplied by this
     logit_cap: Optional[float] = None         # logits <- cap * tanh(logits / cap)
+    logit_scale: float = 1.0                  # logits <- logits * this (before a cap)
 
     def validate(self) -> None:
         if not self.blocks or not self.schedule:

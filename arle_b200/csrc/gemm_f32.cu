@@ -94,3 +94,82 @@ ARLE_API int arle_gemm_plain_bf16(const void* A, const void* W, void* C, int c_d
   if (c_dtype == 0) return launch_plain<__nv_bfloat16, __nv_bfloat16, float>(A, W, C, M, N, K, lda, ldw, ldc, s);
   return ARLE_E_BADARG;
 }
+
+// The same product once per head, heads side by side in a row: C[m, h, n] = sum_k A[m, h, k] . W[h, n, k], head h of a row
+// starting a_head / w_head / c_head elements after head h - 1.  Small per-head matrices (a latent attention's key and
+// value maps folded into its queries and outputs); k ascending as above, so a row's result does not depend on M.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) gemm_heads_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
+                                                         int M, int N, int K, int lda, int ldw, int ldc, int a_head, long w_head,
+                                                         int c_head) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  A += (size_t)blockIdx.z * a_head;
+  W += (size_t)blockIdx.z * w_head;
+  C += (size_t)blockIdx.z * c_head;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx >> 4, c = idx & 15;
+      const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+      As[c][r] = (gm < M && gk < K) ? to_f32(A[(size_t)gm * lda + gk]) : 0.f;
+      Ws[c][r] = (gn < N && gk < K) ? to_f32(W[(size_t)gn * ldw + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) C[(size_t)gm * ldc + gn] = from_f32<TC>(acc[i][j]);
+    }
+  }
+}
+
+// dtype: 0 float32 A and C (W float32 or bfloat16 by w_dtype), 1 bfloat16 A, W and C.
+ARLE_API int arle_gemm_heads(const void* A, const void* W, void* C, int dtype, int w_dtype, int M, int N, int K, int heads,
+                             int lda, int ldw, int ldc, int a_head, long w_head, int c_head, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || heads <= 0) return 0;
+  if (K <= 0) return ARLE_E_BADARG;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
+  if (grid.y > 65535 || heads > 65535) return ARLE_E_UNSUPPORTED;
+  if (dtype == 0 && w_dtype == 0)
+    launch_kernel(gemm_heads_kernel<float, float, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A, (const float*)W,
+                  (float*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
+  else if (dtype == 0 && w_dtype == 1)
+    launch_kernel(gemm_heads_kernel<float, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A,
+                  (const __nv_bfloat16*)W, (float*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
+  else if (dtype == 1 && w_dtype == 1)
+    launch_kernel(gemm_heads_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1,
+                  (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, a_head, w_head, c_head);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

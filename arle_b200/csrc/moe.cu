@@ -1,0 +1,256 @@
+// A feed-forward of routed experts.
+//
+//  * moe_select: from a token's float32 router sums z: scores s = sigmoid(z); choice scores s + correction; the experts
+//    stand in `groups` equal groups of neighbours, a group's score is the sum of its two largest choice scores (its one
+//    score when a group is a single expert), only experts of the `keep` best groups can be chosen (the others count as
+//    minus infinity); the `top` largest choice scores are chosen and weighted with s * scale (no renormalisation).
+//    Ties go to the lower index.  One thread per token, everything float32.
+//  * moe_plan: sorts the step's (token, choice) pairs by expert (counts, offsets, a place for every pair) and lists
+//    the tiles of 64 places that the grouped product runs, one block of 1,024 threads; nothing goes through the host,
+//    so the step can be captured in a graph.  The order of the pairs inside an expert's run is whatever the
+//    atomics gave; no result depends on it, since every place is computed alone.
+//  * moe_gemm: C[place, :] = A[row(place), :] . W[expert(place)]^T in tiles of 64 x 64, float32 sums with k ascending
+//    (the per-expert twin of the plain product).  `rows` maps a place to its row of A (the token of the pair) or is
+//    absent (A is already in place order).
+//  * moe_combine: out[t] = sum_k weight[t, k] * Y[place(t, k)] (k ascending) + sigmoid(gate[t]) * shared[t].
+#include "common.cuh"
+using namespace arle;
+
+__global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ correction,
+                                  float* __restrict__ scratch, int E, int top, int groups, int keep, float scale,
+                                  int* __restrict__ ids, float* __restrict__ wts, int num_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= num_tokens) return;
+  const float* zr = z + (size_t)t * z_stride;
+  float* ch = scratch + (size_t)t * (E + groups);       // choice scores, then the groups' scores
+  float* gs = ch + E;
+  for (int e = 0; e < E; ++e) ch[e] = 1.0f / (1.0f + expf(-zr[e])) + (correction ? correction[e] : 0.f);
+  const int per = E / groups;
+  for (int g = 0; g < groups; ++g) {
+    float b1 = -INFINITY, b2 = -INFINITY;
+    for (int i = 0; i < per; ++i) {
+      const float v = ch[g * per + i];
+      if (v > b1) {
+        b2 = b1;
+        b1 = v;
+      } else if (v > b2) {
+        b2 = v;
+      }
+    }
+    gs[g] = per > 1 ? b1 + b2 : b1;
+  }
+  if (keep < groups) {
+    // the groups that are not kept: all but the `keep` best
+    for (int it = 0; it < keep; ++it) {
+      int bi = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < groups; ++g) {
+        const float v = gs[g];
+        if (v != INFINITY && (bi < 0 || v > bv)) {
+          bv = v;
+          bi = g;
+        }
+      }
+      gs[bi] = INFINITY;                                // marks a kept group
+    }
+    for (int g = 0; g < groups; ++g)
+      if (gs[g] != INFINITY)
+        for (int i = 0; i < per; ++i) ch[g * per + i] = -INFINITY;
+  }
+  for (int it = 0; it < top; ++it) {
+    int bi = -1;
+    float bv = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      const float v = ch[e];
+      if (v != INFINITY && (bi < 0 || v > bv)) {
+        bv = v;
+        bi = e;
+      }
+    }
+    ch[bi] = INFINITY;                                  // taken
+    ids[(size_t)t * top + it] = bi;
+    wts[(size_t)t * top + it] = scale / (1.0f + expf(-zr[bi]));
+  }
+}
+
+ARLE_API int arle_moe_select(const float* z, int z_stride, const float* correction, float* scratch, int E, int top, int groups,
+                             int keep, float scale, int* ids, float* wts, int num_tokens, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || groups <= 0 || E % groups || keep <= 0 || keep > groups || top > keep * (E / groups)) return ARLE_E_BADARG;
+  launch_kernel(moe_select_kernel, dim3((num_tokens + 63) / 64), dim3(64), 0, s, 1, z, z_stride, correction, scratch, E, top, groups,
+                keep, scale, ids, wts, num_tokens);
+  return launch_status();
+}
+
+constexpr int kMoeTile = 64;
+constexpr int kMoeMaxExperts = 1024;
+
+// plan (int32): [0, E] offsets of the experts' runs; [E + 1] tiles in use; then per tile (expert, first place, places).
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int pairs, int top, int E, int* __restrict__ plan,
+                                                        int* __restrict__ place_of_pair, int* __restrict__ row_of_place, int max_tiles) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int count[kMoeMaxExperts], offset[kMoeMaxExperts + 1], cursor[kMoeMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    int* tt = plan + E + 2;
+    for (int e = 0; e < E; ++e) {
+      offset[e] = at;
+      plan[e] = at;
+      for (int r0 = 0; r0 < count[e] && tiles < max_tiles; r0 += kMoeTile, ++tiles) {
+        tt[3 * tiles] = e;
+        tt[3 * tiles + 1] = at + r0;
+        tt[3 * tiles + 2] = min(kMoeTile, count[e] - r0);
+      }
+      at += count[e];
+    }
+    offset[E] = at;
+    plan[E] = at;
+    plan[E + 1] = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    const int place = offset[e] + atomicAdd(&cursor[e], 1);
+    place_of_pair[p] = place;
+    row_of_place[place] = p / top;
+  }
+}
+
+ARLE_API int arle_moe_plan_ints(int E, int pairs) { return E + 2 + 3 * (pairs / kMoeTile + E + 1); }
+
+ARLE_API int arle_moe_plan(const int* ids, int pairs, int top, int E, int* plan, int* place_of_pair, int* row_of_place,
+                           cudaStream_t s) {
+  if (pairs <= 0) return 0;
+  if (E <= 0 || E > kMoeMaxExperts || top <= 0) return ARLE_E_UNSUPPORTED;
+  launch_kernel(moe_plan_kernel, dim3(1), dim3(1024), 0, s, 1, ids, pairs, top, E, plan, place_of_pair, row_of_place,
+                pairs / kMoeTile + E + 1);
+  return launch_status();
+}
+
+constexpr int GM = 64, GN = 64, GK = 16;
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ rows,
+                                                       const TW* __restrict__ W, int ldw, long w_expert, TC* __restrict__ C, int ldc,
+                                                       const int* __restrict__ plan, int E, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[E + 1]) return;
+  const int* tt = plan + E + 2 + 3 * tile;
+  const int expert = tt[0], p0 = tt[1], M = tt[2];
+  __shared__ float As[GK][GM + 4];
+  __shared__ float Ws[GK][GN + 4];
+  __shared__ int arow[GM];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int n0 = blockIdx.x * GN;
+  if (tid < GM) arow[tid] = tid < M ? (rows ? rows[p0 + tid] : p0 + tid) : -1;
+  __syncthreads();
+  W += (size_t)expert * w_expert;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx >> 4, c = idx & 15;
+      const int gn = n0 + r, gk = k0 + c;
+      const int ar = arow[r];
+      As[c][r] = (ar >= 0 && gk < K) ? to_f32(A[(size_t)ar * lda + gk]) : 0.f;
+      Ws[c][r] = (gn < N && gk < K) ? to_f32(W[(size_t)gn * ldw + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) C[(size_t)(p0 + m) * ldc + gn] = from_f32<TC>(acc[i][j]);
+    }
+  }
+}
+
+// dtype: type of A and C; w_dtype: type of W [E][N][K] (an expert every w_expert elements).  pairs: places in all.
+ARLE_API int arle_moe_gemm(const void* A, int lda, const int* rows, const void* W, int ldw, long w_expert, void* C, int ldc,
+                           int dtype, int w_dtype, const int* plan, int E, int pairs, int N, int K, cudaStream_t s) {
+  if (pairs <= 0 || N <= 0) return 0;
+  if (K <= 0 || E <= 0) return ARLE_E_BADARG;
+  const int max_tiles = pairs / kMoeTile + E + 1;
+  if (max_tiles > 65535) return ARLE_E_UNSUPPORTED;
+  dim3 grid((N + GN - 1) / GN, max_tiles);
+  if (dtype == 0 && w_dtype == 0)
+    launch_kernel(moe_gemm_kernel<float, float, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A, lda, rows, (const float*)W, ldw,
+                  w_expert, (float*)C, ldc, plan, E, N, K);
+  else if (dtype == 0 && w_dtype == 1)
+    launch_kernel(moe_gemm_kernel<float, __nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A, lda, rows,
+                  (const __nv_bfloat16*)W, ldw, w_expert, (float*)C, ldc, plan, E, N, K);
+  else if (dtype == 1 && w_dtype == 1)
+    launch_kernel(moe_gemm_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1, (const __nv_bfloat16*)A,
+                  lda, rows, (const __nv_bfloat16*)W, ldw, w_expert, (__nv_bfloat16*)C, ldc, plan, E, N, K);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, int y_stride, const int* __restrict__ place_of_pair,
+                                   const float* __restrict__ wts, int top, const T* __restrict__ shared, int shared_stride,
+                                   const float* __restrict__ gate, int gate_stride, T* __restrict__ out, int out_stride, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float g = 1.f;
+  if (shared && gate) g = 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride]));
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(wts[(size_t)t * top + k], to_f32(y[(size_t)place_of_pair[(size_t)t * top + k] * y_stride + c]), acc);
+    if (shared) acc = fmaf(g, to_f32(shared[(size_t)t * shared_stride + c]), acc);
+    out[(size_t)t * out_stride + c] = from_f32<T>(acc);
+  }
+}
+
+ARLE_API int arle_moe_combine(const void* y, int y_stride, const int* place_of_pair, const float* wts, int top, const void* shared,
+                              int shared_stride, const float* gate, int gate_stride, void* out, int out_stride, int dtype,
+                              int num_tokens, int width, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (width <= 0 || top <= 0) return ARLE_E_BADARG;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == 0)
+    launch_kernel(moe_combine_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, (const float*)y, y_stride, place_of_pair, wts, top,
+                  (const float*)shared, shared_stride, gate, gate_stride, (float*)out, out_stride, width);
+  else if (dtype == 1)
+    launch_kernel(moe_combine_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, (const __nv_bfloat16*)y, y_stride,
+                  place_of_pair, wts, top, (const __nv_bfloat16*)shared, shared_stride, gate, gate_stride, (__nv_bfloat16*)out,
+                  out_stride, width);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

@@ -169,3 +169,43 @@ ARLE_API int arle_residual_add(float* resid, const void* delta, int act_dtype, i
     return ARLE_E_BADARG;
   return launch_status();
 }
+
+// Dynamic Tanh in the place of a norm: out = tanh(alpha * x) * weight + bias, element by element, with the same
+// residual sum in front of it as the RMSNorm above (x = resid (+ delta), resid = x when write_resid).  No mean and no
+// variance are formed, so a row needs no reduction; float32 arithmetic, rounded once at the store.
+template <typename TA>
+__global__ void dyt_norm_kernel(float* __restrict__ resid, const TA* __restrict__ delta, const int* __restrict__ rows,
+                                const float* __restrict__ weight, const float* __restrict__ bias, float alpha,
+                                TA* __restrict__ out, int hidden, int write_resid) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* xr = resid + (size_t)r * hidden;
+  const TA* dr = delta ? delta + (size_t)r * hidden : nullptr;
+  TA* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float x = xr[c];
+    if (dr) {
+      x += to_f32(dr[c]);
+      if (write_resid) xr[c] = x;
+    }
+    o[c] = from_f32<TA>(fmaf(tanhf(alpha * x), weight[c], bias ? bias[c] : 0.f));
+  }
+}
+
+ARLE_API int arle_dyt_norm(float* resid, const void* delta, const int* rows, const float* weight, const float* bias,
+                           float alpha, void* out, int act_dtype, int n_out, int hidden, int write_resid, cudaStream_t s) {
+  if (n_out <= 0) return 0;
+  if (hidden <= 0) return ARLE_E_BADARG;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (act_dtype == 0)
+    launch_kernel(dyt_norm_kernel<float>, dim3(n_out), dim3(threads), 0, s, 1, resid, (const float*)delta, rows, weight, bias,
+                  alpha, (float*)out, hidden, write_resid);
+  else if (act_dtype == 1)
+    launch_kernel(dyt_norm_kernel<__nv_bfloat16>, dim3(n_out), dim3(threads), 0, s, 1, resid, (const __nv_bfloat16*)delta, rows,
+                  weight, bias, alpha, (__nv_bfloat16*)out, hidden, write_resid);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

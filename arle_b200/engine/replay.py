@@ -30,7 +30,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to 64); sizes the cache")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (must divide 64)")
-    ap.add_argument("--max-live", type=int, default=8, help="most requests live at a time")
+    ap.add_argument("--max-live", type=int, default=4, help="most requests live at a time")
     ap.add_argument("--kernels", default="fast", choices=["fast", "plain"],
                     help="fast: the kernels serving uses (shapes decide); plain: the general kernels only")
     ap.add_argument("--device", default="cuda:0")

@@ -74,6 +74,20 @@ _SIGNATURES = {
     "arle_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "arle_scatter_tokens": [_P, _P, _P, _I, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+    "arle_dyt_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
+    "arle_gemm_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
+    "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_latent_attention": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "arle_mlstm_gates": [_P, _I, _P, _P, _F, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _I, _I, _P],
+    "arle_mlstm_out": [_P, _P, _P, _I, _I, _P, _F, _P, _I, _I, _I, _I, _P],
+    "arle_ssm_gates": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
+    "arle_conv_silu": [_P, _I, _I, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_gated_group_norm": [_P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P],
+    "arle_moe_select": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _P, _P, _I, _P],
+    "arle_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "arle_moe_gemm": [_P, _I, _P, _P, _I, ctypes.c_long, _P, _I, _I, _I, _P, _I, _I, _I, _I, _P],
+    "arle_moe_combine": [_P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
 }
 
 
@@ -998,3 +1012,292 @@ def gla_out(o, gate, weight, eps: float, scale: float, out, heads: int, vdim: in
         raise KernelError("gla_out: weight must be float32 [vdim]")
     _check(library().arle_gla_out(_ptr(o), _ptr(gate), _dt(out), gate.stride(0) if gate is not None else 0, _ptr(weight),
                                   float(eps), float(scale), _ptr(out), out.stride(0), T, heads, vdim, _stream()), "gla_out")
+
+
+# ------------------------------------------------------------------ a norm without statistics
+def dyt_norm(resid, delta, rows, weight, bias, alpha: float, out, write_resid: bool) -> None:
+    """Dynamic Tanh in a norm's place, with the residual sum of ``rmsnorm`` in front of it: for output row i (source
+    row r = rows[i], or i) x = resid[r] (+ delta[r]); resid[r] = x when write_resid; out[i] = tanh(alpha * x) * weight
+    + bias.  resid float32 [N, H]; delta and out in the activation type; weight, bias float32 [H] (bias may be None)."""
+    H = resid.shape[1]
+    n_out = out.shape[0]
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32 or (bias is not None and bias.dtype != torch.float32):
+        raise KernelError("dyt_norm: residual, weight and bias must be float32")
+    if not (resid.is_contiguous() and out.is_contiguous()) or out.shape[1] != H or weight.numel() != H or (
+            bias is not None and bias.numel() != H):
+        raise KernelError("dyt_norm: bad shapes or strides")
+    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape or not delta.is_contiguous()):
+        raise KernelError("dyt_norm: delta must match the residual's shape and the output's type")
+    if rows is not None:
+        _i32(rows, "rows")
+        if rows.numel() != n_out:
+            raise KernelError("dyt_norm: one output row per entry of rows")
+    elif n_out != resid.shape[0]:
+        raise KernelError("dyt_norm: output rows must match residual rows when no row list is given")
+    _check(library().arle_dyt_norm(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), _ptr(bias), float(alpha), _ptr(out), _dt(out),
+                                   n_out, H, int(bool(write_resid)), _stream()), "dyt_norm")
+
+
+# ------------------------------------------------------------------ attention over latent vectors
+def gemm_heads(x, w, out) -> None:
+    """out[m, h, :] = x[m, h, :] . w[h]^T for every head h: x [M, heads, K], w [heads, N, K] contiguous, out [M, heads, N].
+    x and out may be views into wider rows (any row stride and head stride, unit inner stride).  float32 sums with k
+    ascending in both precisions."""
+    M, heads, K = x.shape
+    N = w.shape[1]
+    if (w.shape[0] != heads or w.shape[2] != K or tuple(out.shape) != (M, heads, N) or not w.is_contiguous()
+            or x.stride(2) != 1 or out.stride(2) != 1 or x.dtype != out.dtype):
+        raise KernelError(f"gemm_heads: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    if x.dtype == torch.bfloat16 and w.dtype != torch.bfloat16:
+        raise KernelError("gemm_heads: bfloat16 rows need bfloat16 matrices")
+    _check(library().arle_gemm_heads(_ptr(x), _ptr(w), _ptr(out), _dt(x), _dt(w), M, N, K, heads, x.stride(0), K, out.stride(0),
+                                     x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
+
+
+def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps: float, inv_freq, rot_dims: int, cache, q_abs, heads: int,
+                dn: int, dr: int, rank: int) -> None:
+    """The per-token preparation of an attention whose cache holds one record [latent | rotated key part] per token.
+    dkv [T, >= rank + dr]: its first ``rank`` numbers are RMS-normed with ``c_weight`` (float32 [rank]), its next ``dr``
+    numbers are rotated (the first ``rot_dims`` of them, element i with i + rot_dims / 2, by position * inv_freq[i]);
+    both go to cache[slot_mapping[t]] (cache [pages, 1, page_size, rank + dr]; None: nothing is stored).  q [T, >= heads
+    * (dn + dr)]: every head's last ``dr`` numbers are rotated the same way into q_abs[t, h, rank:] (q_abs [T, heads,
+    rank + dr], contiguous)."""
+    T = q.shape[0]
+    kd = rank + dr
+    if (q.stride(1) != 1 or dkv.stride(1) != 1 or q.shape[1] < heads * (dn + dr) or dkv.shape[1] < kd or q.dtype != dkv.dtype
+            or tuple(q_abs.shape) != (T, heads, kd) or not q_abs.is_contiguous() or q_abs.dtype != q.dtype):
+        raise KernelError("latent_prep: q, dkv or q_abs do not fit the sizes given")
+    if c_weight.dtype != torch.float32 or c_weight.numel() != rank:
+        raise KernelError("latent_prep: the latent's norm weight must be float32 [rank]")
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise KernelError("latent_prep: inv_freq must be float32 [rot_dims / 2]")
+    if cache is not None:
+        if cache.dtype != q.dtype or cache.shape[1] != 1 or cache.shape[3] != kd or not cache.is_contiguous():
+            raise KernelError(f"latent_prep: cache shape {tuple(cache.shape)} is not [pages, 1, page_size, {kd}] of the activation type")
+        _i32(slot_mapping, "slot_mapping")
+    _i32(positions, "positions")
+    _check(library().arle_latent_prep(_ptr(q), q.stride(0), _ptr(dkv), dkv.stride(0), _dt(q), _ptr(positions),
+                                      _ptr(slot_mapping) if cache is not None else None, _ptr(c_weight), float(eps),
+                                      _ptr(inv_freq) if rot_dims else None, int(rot_dims), _ptr(cache), _ptr(q_abs), heads, dn, dr,
+                                      rank, T, _stream()), "latent_prep")
+
+
+def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank: int, page_size: int, scale: float, window) -> None:
+    """Causal attention of folded queries q_abs [T, heads, kd] over records cache [pages, 1, page_size, kd]: head h's score
+    against record j is (q_abs[t, h] . record_j) * scale, its output sum_j softmax_j * record_j[:rank] (out [T, heads,
+    rank]).  ``window`` None or <= 0: all keys; W: keys p - W + 1 .. p.  float32 arithmetic."""
+    T, heads, kd = q_abs.shape
+    if (not q_abs.is_contiguous() or tuple(out.shape) != (T, heads, rank) or not out.is_contiguous() or out.dtype != q_abs.dtype
+            or cache.dtype != q_abs.dtype or tuple(cache.shape[1:]) != (1, page_size, kd) or not cache.is_contiguous()):
+        raise KernelError("latent_attention: q_abs [T, heads, kd], out [T, heads, rank] and cache [pages, 1, page_size, kd] of one type")
+    _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
+    if block_table.stride(1) != 1:
+        raise KernelError("latent_attention: block table rows must be contiguous")
+    _check(library().arle_latent_attention(_ptr(q_abs), _ptr(out), _ptr(cache), _dt(q_abs), _ptr(positions), _ptr(row_of_token),
+                                           _ptr(block_table), block_table.stride(0), heads, rank, kd, page_size, float(scale),
+                                           int(window) if window else 0, T, _stream()), "latent_attention")
+
+
+# ------------------------------------------------------------------ matrix memories with a scalar decay
+def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads: int, kq_heads: int, dim: int, vdim: int,
+               ones_column: bool, q_scale: float) -> None:
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T (q_t * q_scale) over the tokens of every row of the step (row r owns
+    tokens q_indptr[r] .. q_indptr[r+1]-1), from and into state[state_slots[r]].  q, k [T, kq_heads*dim] (head h reads
+    head h // (heads / kq_heads)), v [T, heads*vdim], in the activation type (views of wider rows are fine); a, b float32
+    [T, heads]; state float32 [slots, n] whose first heads * vcols * dim numbers are the memories, a head's transposed
+    ([heads][vcols][dim]); vcols = vdim + 1 with ``ones_column`` (a column of ones beside v: it carries sum a..b k, the
+    normaliser of a matrix LSTM); out float32 [T, heads, vcols]."""
+    T = v.shape[0]
+    R = state_slots.numel()
+    vcols = vdim + int(bool(ones_column))
+    if (q.shape != (T, kq_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or q.dtype != k.dtype
+            or q.dtype != v.dtype or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1):
+        raise KernelError("decay_scan: q, k [T, kq_heads*dim] and v [T, heads*vdim] of one type with unit inner stride")
+    for t_, n_ in ((a, "a"), (b, "b")):
+        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, heads) or not t_.is_contiguous():
+            raise KernelError(f"decay_scan: {n_} must be contiguous float32 [T, heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < heads * vcols * dim or state.stride(1) != 1:
+        raise KernelError(f"decay_scan: state {tuple(state.shape)} must be float32 [slots, >= {heads * vcols * dim}]")
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, heads, vcols) or not out.is_contiguous():
+        raise KernelError("decay_scan: out must be contiguous float32 [T, heads, vcols]")
+    _i32(q_indptr, "q_indptr"), _i32(state_slots, "state_slots")
+    if q_indptr.numel() != R + 1:
+        raise KernelError("decay_scan: q_indptr must have one entry more than state_slots")
+    _check(library().arle_decay_scan(_ptr(q), _ptr(k), _ptr(v), _dt(q), q.stride(0), k.stride(0), v.stride(0), _ptr(a), _ptr(b),
+                                     _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(state_slots), _ptr(out), R, heads, kq_heads,
+                                     dim, vdim, vcols - vdim, float(q_scale), _stream()), "decay_scan")
+
+
+def mlstm_gates(pre, bias_i, bias_f, cap: float, q_indptr, state_slots, state, m_offset: int, a, b, floor) -> None:
+    """The gates of a matrix LSTM.  pre float32 [T, 2*heads]: the input gates' sums, then the forget gates'.  Per head
+    i = cap tanh((pre_i + bias_i) / cap), f = logsigmoid(cap tanh((pre_f + bias_f) / cap)), the running maximum
+    m_t = max(f + m_(t-1), i) (m of request slot s at state[s, m_offset + head]; it starts at what the slot holds, zero
+    for a new request, and is left at the row's last value), and a = exp(f + m_(t-1) - m_t), b = exp(i - m_t),
+    floor = exp(-m_t), all float32 [T, heads]."""
+    T = pre.shape[0]
+    heads = pre.shape[1] // 2
+    R = state_slots.numel()
+    if pre.dtype != torch.float32 or pre.stride(1) != 1 or pre.shape[1] != 2 * heads:
+        raise KernelError("mlstm_gates: pre must be float32 [T, 2*heads] with unit inner stride")
+    for t_ in (a, b, floor):
+        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, heads) or not t_.is_contiguous():
+            raise KernelError("mlstm_gates: a, b and floor must be contiguous float32 [T, heads]")
+    for t_ in (bias_i, bias_f):
+        if t_ is not None and (t_.dtype != torch.float32 or t_.numel() != heads):
+            raise KernelError("mlstm_gates: biases must be float32 [heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < m_offset + heads or state.stride(1) != 1:
+        raise KernelError("mlstm_gates: state must be float32 [slots, n] and hold the maxima at m_offset")
+    _i32(q_indptr, "q_indptr"), _i32(state_slots, "state_slots")
+    _check(library().arle_mlstm_gates(_ptr(pre), pre.stride(0), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(q_indptr),
+                                      _ptr(state_slots), _ptr(state), state.stride(0), int(m_offset), _ptr(a), _ptr(b), _ptr(floor),
+                                      R, heads, _stream()), "mlstm_gates")
+
+
+def mlstm_out(num, floor, gate, weight, eps: float, out, heads: int, vdim: int) -> None:
+    """out[t, h, :] = rms_unit(num[t, h, :vdim] / (max(|num[t, h, vdim]|, floor[t, h]) + 1e-6)) * weight[h, :] *
+    sigmoid(gate[t, h, :]).  num float32 [T, heads, vdim + 1] (what ``decay_scan`` leaves with its column of ones);
+    gate and out [T, heads*vdim] in the activation type (views of wider rows are fine); weight float32 [heads*vdim]."""
+    T = num.shape[0]
+    if num.dtype != torch.float32 or tuple(num.shape) != (T, heads, vdim + 1) or not num.is_contiguous():
+        raise KernelError("mlstm_out: num must be contiguous float32 [T, heads, vdim + 1]")
+    if (floor.dtype != torch.float32 or tuple(floor.shape) != (T, heads) or not floor.is_contiguous()
+            or weight.dtype != torch.float32 or weight.numel() != heads * vdim):
+        raise KernelError("mlstm_out: floor float32 [T, heads], weight float32 [heads*vdim]")
+    if (tuple(out.shape) != (T, heads * vdim) or gate.shape != out.shape or gate.dtype != out.dtype or gate.stride(1) != 1
+            or out.stride(1) != 1):
+        raise KernelError("mlstm_out: gate and out must be [T, heads*vdim] of one type with unit inner stride")
+    _check(library().arle_mlstm_out(_ptr(num), _ptr(floor), _ptr(gate), _dt(out), gate.stride(0), _ptr(weight), float(eps), _ptr(out),
+                                    out.stride(0), T, heads, vdim, _stream()), "mlstm_out")
+
+
+def ssm_gates(dt_raw, dt_bias, a_log, a, b) -> None:
+    """dt = softplus(dt_raw + dt_bias) (no clamp); a = exp(-exp(a_log) * dt); b = dt.  dt_raw float32 [T, heads] (any row
+    stride); dt_bias, a_log float32 [heads]; a, b contiguous float32 [T, heads]."""
+    T, heads = dt_raw.shape
+    if dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1:
+        raise KernelError("ssm_gates: dt_raw must be float32 with unit inner stride")
+    for t_ in (dt_bias, a_log):
+        if t_.dtype != torch.float32 or t_.numel() != heads:
+            raise KernelError("ssm_gates: dt_bias and a_log must be float32 [heads]")
+    for t_ in (a, b):
+        if t_.dtype != torch.float32 or tuple(t_.shape) != (T, heads) or not t_.is_contiguous():
+            raise KernelError("ssm_gates: a and b must be contiguous float32 [T, heads]")
+    _check(library().arle_ssm_gates(_ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(a), _ptr(b), T, heads, _stream()),
+           "ssm_gates")
+
+
+def conv_silu(x, weight, bias, state, conv_offset: int, q_indptr, row_of_token, state_slots, out) -> None:
+    """out[t, c] = silu(bias[c] + sum_j weight[c, j] * in[t - (taps - 1) + j, c]) over the tokens of t's row; before the row's
+    first token of this step stand the request's last taps - 1 inputs, kept at state[slot, conv_offset + c * (taps - 1) + j]
+    (oldest first; zero for a new request) and brought up to date after the convolution.  x, out [T, C] in the activation
+    type (views of wider rows are fine); weight float32 [C, taps], bias float32 [C] or None; state float32 [slots, n]."""
+    T, C = x.shape
+    taps = weight.shape[1]
+    R = state_slots.numel()
+    if x.stride(1) != 1 or out.stride(1) != 1 or out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("conv_silu: x and out must be [T, C] of one type with unit inner stride")
+    if weight.dtype != torch.float32 or weight.shape[0] != C or not weight.is_contiguous() or (
+            bias is not None and (bias.dtype != torch.float32 or bias.numel() != C)):
+        raise KernelError("conv_silu: weight float32 [C, taps] contiguous, bias float32 [C]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < conv_offset + C * (taps - 1) or state.stride(1) != 1:
+        raise KernelError("conv_silu: state must be float32 [slots, n] with room for C * (taps - 1) numbers at conv_offset")
+    _i32(q_indptr, "q_indptr"), _i32(row_of_token, "row_of_token"), _i32(state_slots, "state_slots")
+    _check(library().arle_conv_silu(_ptr(x), _dt(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(state), state.stride(0),
+                                    int(conv_offset), _ptr(q_indptr), _ptr(row_of_token), _ptr(state_slots), _ptr(out), out.stride(0),
+                                    T, R, C, taps, _stream()), "conv_silu")
+    if taps > 1:
+        add_launches(1)
+
+
+def gated_group_norm(y, x, skip, vdim: int, z, weight, eps: float, out, parts: int) -> None:
+    """out = rms_unit_in_parts((y + skip[head] * x) * silu(z)) * weight: the row of ``inner`` numbers in ``parts`` equal
+    parts, each divided by its own root mean square; head = column // vdim.  y float32 [T, inner] contiguous; x, z, out
+    [T, inner] in the activation type (views of wider rows are fine); skip float32 [inner / vdim] or None (then x is not
+    read); weight float32 [inner]."""
+    T, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or inner % parts:
+        raise KernelError("gated_group_norm: y must be contiguous float32 [T, inner] with inner a multiple of parts")
+    for t_ in ((x, z, out) if skip is not None else (z, out)):
+        if tuple(t_.shape) != (T, inner) or t_.stride(1) != 1 or t_.dtype != out.dtype:
+            raise KernelError("gated_group_norm: x, z and out must be [T, inner] of one type with unit inner stride")
+    if weight.dtype != torch.float32 or weight.numel() != inner or (
+            skip is not None and (skip.dtype != torch.float32 or skip.numel() * vdim != inner)):
+        raise KernelError("gated_group_norm: weight float32 [inner], skip float32 [inner / vdim]")
+    _check(library().arle_gated_group_norm(_ptr(y), _ptr(x) if skip is not None else None, _dt(out),
+                                           x.stride(0) if skip is not None else 0, _ptr(skip), vdim, _ptr(z), z.stride(0),
+                                           _ptr(weight), float(eps), _ptr(out), out.stride(0), T, inner, parts, _stream()),
+           "gated_group_norm")
+
+
+# ------------------------------------------------------------------ routed experts
+def moe_select(z, correction, scratch, experts: int, top: int, groups: int, keep: int, scale: float, ids, weights) -> None:
+    """Chooses ``top`` experts per token from float32 router sums z [T, >= experts] (any row stride): scores sigmoid(z),
+    choice scores with ``correction`` (float32 [experts] or None) added, experts in ``groups`` equal groups of neighbours of
+    which only the ``keep`` with the best scores (sum of a group's two largest choice scores) can be chosen; ids int32
+    [T, top] in the order chosen, weights float32 [T, top] = sigmoid(z) * scale.  scratch float32 [T, experts + groups]."""
+    T = z.shape[0]
+    if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < experts:
+        raise KernelError("moe_select: z must be float32 [T, >= experts] with unit inner stride")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
+        raise KernelError("moe_select: correction must be float32 [experts]")
+    if scratch.dtype != torch.float32 or scratch.numel() < T * (experts + groups) or not scratch.is_contiguous():
+        raise KernelError("moe_select: scratch must be contiguous float32 [T, experts + groups]")
+    if (ids.dtype != torch.int32 or weights.dtype != torch.float32 or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top)
+            or not ids.is_contiguous() or not weights.is_contiguous()):
+        raise KernelError("moe_select: ids int32 [T, top] and weights float32 [T, top], contiguous")
+    _check(library().arle_moe_select(_ptr(z), z.stride(0), _ptr(correction), _ptr(scratch), experts, top, groups, keep, float(scale),
+                                     _ptr(ids), _ptr(weights), T, _stream()), "moe_select")
+
+
+def moe_plan_size(experts: int, pairs: int) -> int:
+    """int32 entries of the plan that ``moe_plan`` writes."""
+    lib = library()
+    lib.arle_moe_plan_ints.argtypes = [c_int, c_int]
+    lib.arle_moe_plan_ints.restype = c_int
+    return int(lib.arle_moe_plan_ints(int(experts), int(pairs)))
+
+
+def moe_plan(ids, experts: int, plan, place_of_pair, row_of_place) -> None:
+    """Sorts the pairs (token, choice) of ids [T, top] by expert, on the device: plan (int32, ``moe_plan_size`` entries: the
+    experts' runs and the tiles the grouped product runs), place_of_pair int32 [T*top], row_of_place int32 [T*top] (the
+    token of the pair at each place)."""
+    T, top = ids.shape
+    pairs = T * top
+    if (ids.dtype != torch.int32 or not ids.is_contiguous() or plan.dtype != torch.int32 or plan.numel() < moe_plan_size(experts, pairs)
+            or place_of_pair.dtype != torch.int32 or place_of_pair.numel() < pairs or row_of_place.dtype != torch.int32
+            or row_of_place.numel() < pairs):
+        raise KernelError("moe_plan: int32 tables of the sizes moe_plan_size gives")
+    _check(library().arle_moe_plan(_ptr(ids), pairs, top, experts, _ptr(plan), _ptr(place_of_pair), _ptr(row_of_place), _stream()),
+           "moe_plan")
+
+
+def moe_gemm(x, rows, w, out, plan, experts: int) -> None:
+    """out[place] = x[rows[place]] . w[expert of place]^T for every place of the plan (rows None: x is in place order).
+    x [*, K], w [experts, N, K] contiguous, out [pairs, N] in x's type; float32 sums, k ascending."""
+    pairs, N = out.shape
+    K = x.shape[1]
+    if (w.dim() != 3 or w.shape[0] != experts or w.shape[1] != N or w.shape[2] != K or not w.is_contiguous() or x.stride(1) != 1
+            or out.stride(1) != 1 or x.dtype != out.dtype or (x.dtype == torch.bfloat16 and w.dtype != torch.bfloat16)):
+        raise KernelError(f"moe_gemm: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    _i32(rows, "rows"), _i32(plan, "plan")
+    _check(library().arle_moe_gemm(_ptr(x), x.stride(0), _ptr(rows), _ptr(w), K, N * K, _ptr(out), out.stride(0), _dt(x), _dt(w),
+                                   _ptr(plan), experts, pairs, N, K, _stream()), "moe_gemm")
+
+
+def moe_combine(y, place_of_pair, weights, shared, gate, out) -> None:
+    """out[t] = sum_k weights[t, k] * y[place_of_pair[t*top + k]] (k ascending, float32) + sigmoid(gate[t]) * shared[t].
+    y [pairs, width]; shared [T, width] or None; gate float32 [T] (any stride) or None (the shared rows are added as
+    they are); out [T, width] (unit inner stride)."""
+    T, top = weights.shape
+    width = out.shape[1]
+    if (y.shape[1] != width or y.stride(1) != 1 or out.stride(1) != 1 or y.dtype != out.dtype or weights.dtype != torch.float32
+            or not weights.is_contiguous() or out.shape[0] != T):
+        raise KernelError("moe_combine: y [pairs, width] and out [T, width] of one type, weights float32 [T, top]")
+    if shared is not None and (tuple(shared.shape) != (T, width) or shared.stride(1) != 1 or shared.dtype != out.dtype):
+        raise KernelError("moe_combine: shared must be [T, width] in the activation type")
+    if gate is not None and (gate.dtype != torch.float32 or gate.numel() != T or gate.dim() != 1):
+        raise KernelError("moe_combine: gate must be float32 [T]")
+    _i32(place_of_pair, "place_of_pair")
+    _check(library().arle_moe_combine(_ptr(y), y.stride(0), _ptr(place_of_pair), _ptr(weights), top, _ptr(shared),
+                                      shared.stride(0) if shared is not None else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                      _ptr(out), out.stride(0), _dt(out), T, width, _stream()), "moe_combine")

@@ -1,10 +1,14 @@
 from .attention import Attention, AttentionSpec
 from .base import Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, StateNeed, WeightDecl
 from .block import PreNormBlock, PreNormBlockSpec
+from .latent_attention import LatentAttention, LatentAttentionSpec
 from .linear_attention import GatedLinearAttention, GatedLinearAttentionSpec
+from .mamba2 import Mamba2, Mamba2Spec
+from .mlstm import MatrixLstm, MatrixLstmSpec
+from .moe import RoutedExperts, RoutedExpertsSpec
 from .mlp import GatedMlp, GatedMlpSpec
 from .model import DecoderModel, ResidualStream, declared_weights
-from .norm import RmsNorm, RmsNormSpec
+from .norm import DynTanh, DynTanhSpec, RmsNorm, RmsNormSpec
 from .parallel import ParallelBlock, ParallelBlockSpec, ParallelMixer, ParallelMixerSpec
 from .registry import build_model, build_part, register_model, register_part, registered_models, registered_parts
 from .rotary import Rotary, RotarySpec
@@ -12,5 +16,6 @@ from .rotary import Rotary, RotarySpec
 __all__ = ["Attention", "AttentionSpec", "Block", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part",
            "PositionEncoding", "StateNeed", "WeightDecl", "PreNormBlock", "PreNormBlockSpec", "GatedMlp",
            "GatedMlpSpec", "GatedLinearAttention", "GatedLinearAttentionSpec", "ParallelBlock", "ParallelBlockSpec",
-           "ParallelMixer", "ParallelMixerSpec", "DecoderModel", "ResidualStream", "declared_weights", "RmsNorm", "RmsNormSpec",
+           "ParallelMixer", "ParallelMixerSpec", "LatentAttention", "LatentAttentionSpec", "Mamba2", "Mamba2Spec", "MatrixLstm",
+           "MatrixLstmSpec", "RoutedExperts", "RoutedExpertsSpec", "DynTanh", "DynTanhSpec", "DecoderModel", "ResidualStream", "declared_weights", "RmsNorm", "RmsNormSpec",
            "build_model", "build_part", "register_model", "register_part", "registered_models", "registered_parts", "Rotary", "RotarySpec"]

@@ -1,4 +1,5 @@
-"""Pre-norm block: x <- x + mixer(norm(x)); x <- x + ffn(norm(x))
+"""Pre-norm block: x <- x + mixer(norm(x)); x <- x + ffn(norm(x)) (the second half is absent when the spec names no
+feed-forward)
 (infer/src/model/qwen3/prefill.rs:618-776).  The block never touches the residual
 itself: it hands branch outputs to the ``ResidualStream``, which folds each into
 the 32-bit residual inside the kernel of the next norm, the fusion cklxx/arle's
@@ -16,8 +17,8 @@ from .registry import build_part, register_part
 class PreNormBlockSpec:
     mixer_norm: object
     mixer: object
-    ffn_norm: object
-    ffn: object
+    ffn_norm: object = None         # None together with ffn: the block is its mixer half alone
+    ffn: object = None
     kind: ClassVar[str] = "prenorm_block"
 
 
@@ -26,9 +27,11 @@ class PreNormBlock(Block):
         self.spec = spec
         self.mixer_norm = build_part(spec.mixer_norm)
         self.mixer = build_part(spec.mixer)
-        self.ffn_norm = build_part(spec.ffn_norm)
-        self.ffn = build_part(spec.ffn)
-        self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        if (spec.ffn is None) != (spec.ffn_norm is None):
+            raise ValueError("a pre-norm block has a feed-forward and its norm, or neither")
+        self.ffn_norm = build_part(spec.ffn_norm) if spec.ffn_norm is not None else None
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
 
     def weight_decls(self):
         return tuple(d for p in self._parts for d in p.weight_decls())
@@ -42,6 +45,8 @@ class PreNormBlock(Block):
 
     def scratch_elements_per_token(self):
         # the two normalised inputs and the larger of the two branches' buffers
+        if self.ffn is None:
+            return self.mixer_norm.scratch_elements_per_token() + self.mixer.scratch_elements_per_token()
         return (self.mixer_norm.scratch_elements_per_token() + self.ffn_norm.scratch_elements_per_token()
                 + max(self.mixer.scratch_elements_per_token(), self.ffn.scratch_elements_per_token()))
 
@@ -51,6 +56,11 @@ class PreNormBlock(Block):
     def forward(self, stream, ctx, cache, state):
         T = ctx.num_tokens
         h = stream.normed(self.mixer_norm, "normed_a")
+        if self.ffn is None:
+            nxt = stream.next_entry
+            sink = stream.sink_for(nxt[0], nxt[1], "normed_a") if nxt is not None and self.mixer.can_sink(T) else None
+            stream.add(self.mixer.forward(h, ctx, cache, state, sink=sink) if sink is not None else self.mixer.forward(h, ctx, cache, state))
+            return
         # where a branch's last product can add into the residual and leave the next norm's input behind,
         # and that norm's reader can apply the norm's factor itself, the norm between them is no kernel
         sink = stream.sink_for(self.ffn_norm, self.ffn, "normed_b") if self.mixer.can_sink(T) else None

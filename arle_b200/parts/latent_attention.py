@@ -1,0 +1,140 @@
+"""Attention whose cache holds one latent vector per token instead of keys and values per head.
+
+    q = W_q x                       per head [dn unrotated | dr rotated]
+    W_dkv x = [c_raw | k_rot_raw]   rank + dr numbers; c = rmsnorm(c_raw) * weight, k_rot = rotate(k_rot_raw)
+    head h:  k_h = [W_uk[h] c | k_rot],  v_h = W_uv[h] c
+    score = (q_nope . W_uk[h] c + rotate(q_rot) . k_rot) * scale;  softmax over the visible keys;  out = W_o [heads' sums]
+
+Only c and k_rot are cached: one record of rank + dr numbers per token, one stream of one head in the paged
+cache.  The keys and values are never built.  Since q_nope . (W_uk[h] c) = (W_uk[h]^T q_nope) . c, the heads' key
+maps are folded into the queries (one small product per head), every head then attends over the same records with
+keys [c | k_rot] and values c, and W_uv[h] is applied to the head's weighted sum of latents afterwards.  The
+position encoding is the rotary part's (pairing "half"); it turns the first ``rotary_dim`` of the dr numbers.
+A ``window`` keeps the last ``window`` positions visible (itself included) and lets older pages go back.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar, Optional, Tuple
+
+import torch
+
+from .. import ops
+from .base import CacheNeed, Mixer, WeightDecl
+from .registry import build_part, register_part
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    prefix: str
+    hidden_size: int
+    num_heads: int
+    nope_dim: int                   # unrotated query/key numbers per head
+    rope_dim: int                   # rotated query/key numbers per head (the key's are shared by the heads)
+    value_dim: int                  # per head
+    kv_rank: int                    # size of the latent
+    scale: float
+    norm_eps: float                 # of the latent's RMSNorm
+    position: Optional[object]      # a rotary spec (its rotary_dim <= rope_dim) or None
+    window: Optional[int] = None
+    names: Optional[Tuple[Tuple[str, str], ...]] = None    # (role, name after the prefix); see DEFAULT_NAMES
+    kind: ClassVar[str] = "latent_attention"
+
+
+DEFAULT_NAMES = (("q", "q"), ("dkv", "dkv"), ("latent_norm", "dkv.norm"), ("uk", "uk"), ("uv", "uv"), ("o", "o"))
+
+
+class LatentAttention(Mixer):
+    def __init__(self, spec: LatentAttentionSpec):
+        if min(spec.num_heads, spec.value_dim, spec.kv_rank) <= 0 or spec.nope_dim < 0 or spec.rope_dim < 0 or spec.nope_dim + spec.rope_dim <= 0:
+            raise ValueError("latent attention: heads, value_dim and kv_rank must be positive, nope_dim + rope_dim too")
+        if spec.kv_rank > 512:
+            raise ValueError(f"latent attention: kv_rank {spec.kv_rank} not supported (at most 512)")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("window must be positive")
+        self.spec = spec
+        self.position = build_part(spec.position) if spec.position is not None else None
+        if self.position is not None and (getattr(self.position, "pairing", "half") != "half"
+                                          or self.position.spec.rotary_dim > spec.rope_dim):
+            raise ValueError("latent attention: the rotation pairs element i with i + dims/2 and turns at most rope_dim numbers")
+        self.names = dict(DEFAULT_NAMES)
+        self.names.update(dict(spec.names or ()))
+        self.q_width = spec.num_heads * (spec.nope_dim + spec.rope_dim)
+        self.record = spec.kv_rank + spec.rope_dim
+        self.rows = -(-(self.q_width + self.record) // 8) * 8
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.latent_norm = None
+
+    def _name(self, role: str) -> str:
+        return self.spec.prefix + self.names[role]
+
+    # ---------------------------------------------------------------- weights
+    def weight_decls(self):
+        s = self.spec
+        return (WeightDecl(self._name("q"), (self.q_width, s.hidden_size)), WeightDecl(self._name("dkv"), (self.record, s.hidden_size)),
+                WeightDecl(self._name("latent_norm"), (s.kv_rank,), init="gain"),
+                WeightDecl(self._name("uk"), (s.num_heads * s.nope_dim, s.kv_rank)),
+                WeightDecl(self._name("uv"), (s.num_heads * s.value_dim, s.kv_rank)),
+                WeightDecl(self._name("o"), (s.hidden_size, s.num_heads * s.value_dim)))
+
+    def load(self, tensors, dtype, device):
+        s = self.spec
+        mats = [tensors[self._name("q")], tensors[self._name("dkv")]]
+        pad = self.rows - sum(m.shape[0] for m in mats)
+        if pad:
+            mats.append(torch.zeros((pad, s.hidden_size), dtype=mats[0].dtype))
+
+        def kept(ts):
+            return dtype if dtype == torch.bfloat16 else (torch.float32 if any(t.dtype == torch.float32 for t in ts) else torch.bfloat16)
+
+        self.w_in = torch.cat([m.to(device=device, dtype=kept(mats)) for m in mats], dim=0).contiguous()
+        uk, uv, o = (tensors[self._name(n)] for n in ("uk", "uv", "o"))
+        # head h's key map transposed: [rank, nope_dim], the matrix that folds it into the head's query
+        self.w_uk_t = uk.to(device=device, dtype=kept([uk])).view(s.num_heads, s.nope_dim, s.kv_rank).transpose(1, 2).contiguous()
+        self.w_uv = uv.to(device=device, dtype=kept([uv])).view(s.num_heads, s.value_dim, s.kv_rank).contiguous()
+        self.w_o = o.to(device=device, dtype=kept([o])).contiguous()
+        self.latent_norm = tensors[self._name("latent_norm")].to(device=device, dtype=torch.float32).contiguous()
+        if self.position is not None:
+            self.position.load(tensors, dtype, device)
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_uk_t, self.w_uv, self.w_o))
+
+    def scratch_elements_per_token(self):
+        s = self.spec
+        return self.rows + s.num_heads * (self.record + s.kv_rank + s.value_dim) + s.hidden_size
+
+    # ------------------------------------------------------------------ cache
+    def cache_need(self):
+        return CacheNeed(window=self.spec.window, streams=((1, self.record),))
+
+    def can_sink(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_o)
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, x, ctx, cache, state, sink=None):
+        s = self.spec
+        T = x.shape[0]
+        H, dn, dr, rank = s.num_heads, s.nope_dim, s.rope_dim, s.kv_rank
+        rot = self.position.rotary() if self.position is not None else None
+        inv_freq, rdim = rot if rot is not None else (None, 0)
+        proj = ctx.ws.get("latent_in", (T, self.rows), x.dtype)
+        ops.gemm(x, self.w_in, proj)
+        q = proj[:, : self.q_width]
+        q_abs = ctx.ws.get("latent_q", (T, H, self.record), x.dtype)
+        records = cache.streams[0]
+        ops.latent_prep(q, proj[:, self.q_width: self.q_width + self.record], ctx.positions, cache.slot_mapping, self.latent_norm,
+                        s.norm_eps, inv_freq, rdim, records if cache.writable else None, q_abs, H, dn, dr, rank)
+        if dn:
+            ops.gemm_heads(q.unflatten(1, (H, dn + dr))[:, :, :dn], self.w_uk_t, q_abs[:, :, :rank])
+        else:
+            q_abs[:, :, :rank].zero_()
+        o_lat = ctx.ws.get("latent_o", (T, H, rank), x.dtype)
+        ops.latent_attention(q_abs, o_lat, records, ctx.positions, ctx.row_of_token, cache.block_table, rank, cache.page_size,
+                             s.scale, s.window)
+        heads_out = ctx.ws.get("attn_out", (T, H, s.value_dim), x.dtype)
+        ops.gemm_heads(o_lat, self.w_uv, heads_out)
+        out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
+        return None if ops.gemm(heads_out.view(T, H * s.value_dim), self.w_o, out, sink=sink) else out
+
+
+register_part(LatentAttentionSpec.kind, LatentAttention)

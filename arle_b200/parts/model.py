@@ -186,6 +186,8 @@ class DecoderModel:
         final = stream.normed_rows(self.final_norm, ctx.want_rows, "final_normed")
         logits = ctx.ws.get("logits", (ctx.num_wanted, self.spec.vocab_size), torch.float32)
         ops.gemm(final, self.head, logits)
+        if self.spec.logit_scale != 1.0:
+            ops.weighted_sum(logits, self.spec.logit_scale, logits, 0.0, logits)
         if self.spec.logit_cap:
             ops.logit_cap(logits, self.spec.logit_cap)
         return logits

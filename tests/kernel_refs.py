@@ -254,5 +254,180 @@ def rotary_angles(positions, inv_freq, out):
     out.copy_(torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1))
 
 
+# ---------------------------------------------------------------- Dynamic Tanh
+def dyt_norm(resid, delta, rows, weight, bias, alpha, out, write_resid):
+    idx = rows.long() if rows is not None else torch.arange(resid.shape[0], device=resid.device)
+    x = resid[idx].to(F32)
+    if delta is not None:
+        x = x + delta[idx].to(F32)
+        if write_resid:
+            resid[idx] = x
+    y = torch.tanh(alpha * x) * weight
+    out.copy_((y + bias if bias is not None else y).to(out.dtype))
+
+
+# ---------------------------------------------------------------- attention over latent vectors
+def gemm_heads(x, w, out):
+    out.copy_(torch.einsum("mhk,hnk->mhn", x.to(F32), w.to(F32)).to(out.dtype))
+
+
+def _turn_half(x, pos, inv_freq, dims):
+    """x [T, ..., D]: the first ``dims`` elements turn, i with i + dims/2."""
+    if not dims:
+        return x
+    half = dims // 2
+    ang = pos.to(F32)[:, None] * inv_freq[None, :]
+    while ang.dim() < x.dim():
+        ang = ang.unsqueeze(1)
+    c, s_ = torch.cos(ang), torch.sin(ang)
+    u, v = x[..., :half], x[..., half:dims]
+    return torch.cat([u * c - v * s_, v * c + u * s_, x[..., dims:]], dim=-1)
+
+
+def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps, inv_freq, rot_dims, cache, q_abs, heads, dn, dr, rank):
+    T = q.shape[0]
+    kv = dkv[:, : rank + dr].to(F32)
+    if cache is not None:
+        c = kv[:, :rank]
+        c = c * (1.0 / torch.sqrt((c * c).mean(dim=-1, keepdim=True) + eps)) * c_weight
+        rec = torch.cat([c, _turn_half(kv[:, rank:], positions, inv_freq, rot_dims)], dim=-1).to(cache.dtype)
+        page_size = cache.shape[2]
+        sm = slot_mapping.long()
+        cache[sm // page_size, 0, sm % page_size] = rec
+    qr = q[:, : heads * (dn + dr)].to(F32).view(T, heads, dn + dr)[:, :, dn:]
+    q_abs[:, :, rank:] = _turn_half(qr, positions, inv_freq, rot_dims).to(q_abs.dtype)
+
+
+def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank, page_size, scale, window):
+    T, H, kd = q_abs.shape
+    for t in range(T):
+        p = int(positions[t])
+        lo = max(0, p - window + 1) if window else 0
+        js = torch.arange(lo, p + 1)
+        pages = block_table[int(row_of_token[t]), js // page_size].long()
+        rec = cache[pages, 0, js % page_size].to(F32)          # [n, kd]
+        pr = torch.softmax((q_abs[t].to(F32) @ rec.t()) * scale, dim=-1)
+        out[t] = (pr @ rec[:, :rank]).to(out.dtype)
+
+
+# ---------------------------------------------------------------- matrix memories with a scalar decay
+def decay_scan(q, k, v, a, b, state, q_indptr, state_slots, out, heads, kq_heads, dim, vdim, ones_column, q_scale):
+    vcols = vdim + int(bool(ones_column))
+    rep = heads // kq_heads
+    for r in range(state_slots.numel()):
+        S = state[int(state_slots[r]), : heads * vcols * dim].view(heads, vcols, dim)
+        for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+            qt = q[t].to(F32).view(kq_heads, dim).repeat_interleave(rep, dim=0) * q_scale
+            kt = k[t].to(F32).view(kq_heads, dim).repeat_interleave(rep, dim=0)
+            vt = v[t].to(F32).view(heads, vdim)
+            if ones_column:
+                vt = torch.cat([vt, torch.ones(heads, 1)], dim=1)
+            S.copy_(S * a[t][:, None, None] + (b[t][:, None] * vt)[:, :, None] * kt[:, None, :])
+            out[t] = torch.einsum("hvd,hd->hv", S, qt)
+
+
+def mlstm_gates(pre, bias_i, bias_f, cap, q_indptr, state_slots, state, m_offset, a, b, floor):
+    H = pre.shape[1] // 2
+    gi = cap * torch.tanh((pre[:, :H] + bias_i) / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((pre[:, H:] + bias_f) / cap))
+    for r in range(state_slots.numel()):
+        m = state[int(state_slots[r]), m_offset: m_offset + H]
+        for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+            m_new = torch.maximum(gf[t] + m, gi[t])
+            a[t] = torch.exp(gf[t] + m - m_new)
+            b[t] = torch.exp(gi[t] - m_new)
+            floor[t] = torch.exp(-m_new)
+            m.copy_(m_new)
+
+
+def mlstm_out(num, floor, gate, weight, eps, out, heads, vdim):
+    T = num.shape[0]
+    o = num[:, :, :vdim] / (torch.maximum(num[:, :, vdim].abs(), floor) + 1e-6)[:, :, None]
+    o = o * (1.0 / torch.sqrt((o * o).mean(dim=-1, keepdim=True) + eps))
+    o = o.reshape(T, heads * vdim) * weight * torch.sigmoid(gate.to(F32))
+    out.copy_(o.to(out.dtype))
+
+
+def ssm_gates(dt_raw, dt_bias, a_log, a, b):
+    dt = torch.nn.functional.softplus(dt_raw + dt_bias)
+    a.copy_(torch.exp(-torch.exp(a_log) * dt))
+    b.copy_(dt)
+
+
+def conv_silu(x, weight, bias, state, conv_offset, q_indptr, row_of_token, state_slots, out):
+    C, taps = weight.shape
+    for r in range(state_slots.numel()):
+        beg, end = int(q_indptr[r]), int(q_indptr[r + 1])
+        hist = state[int(state_slots[r]), conv_offset: conv_offset + C * (taps - 1)].view(C, taps - 1)
+        seq = torch.cat([hist.t(), x[beg:end].to(F32)], dim=0)               # [taps - 1 + n, C]
+        acc = bias[None, :].repeat(end - beg, 1) if bias is not None else torch.zeros(end - beg, C)
+        for j in range(taps):
+            acc = acc + seq[j: j + end - beg] * weight[:, j][None, :]
+        out[beg:end] = (acc / (1.0 + torch.exp(-acc))).to(out.dtype)
+        if taps > 1:
+            hist.copy_(seq[seq.shape[0] - (taps - 1):].t())
+
+
+def gated_group_norm(y, x, skip, vdim, z, weight, eps, out, parts):
+    T, inner = y.shape
+    v = y
+    if skip is not None:
+        v = v + skip.repeat_interleave(vdim)[None, :] * x.to(F32)
+    g = z.to(F32)
+    v = (v * (g / (1.0 + torch.exp(-g)))).view(T, parts, inner // parts)
+    v = v * (1.0 / torch.sqrt((v * v).mean(dim=-1, keepdim=True) + eps))
+    out.copy_((v.reshape(T, inner) * weight).to(out.dtype))
+
+
+# ---------------------------------------------------------------- routed experts
+def moe_select(z, correction, scratch, experts, top, groups, keep, scale, ids, weights):
+    s_ = torch.sigmoid(z[:, :experts])
+    ch = s_ + correction if correction is not None else s_.clone()
+    per = experts // groups
+    g = ch.view(-1, groups, per)
+    gs = g.topk(min(2, per), dim=-1).values.sum(-1)
+    kept = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gs.topk(keep, dim=-1).indices, True)
+    ch = torch.where(kept[:, :, None].expand(-1, -1, per).reshape(-1, experts), ch, torch.full_like(ch, -math.inf))
+    pick = ch.topk(top, dim=-1).indices
+    ids.copy_(pick.to(torch.int32))
+    weights.copy_(s_.gather(1, pick) * scale)
+
+
+def moe_plan_size(experts, pairs):
+    return experts + 2 + 3 * (pairs // 64 + experts + 1)
+
+
+def moe_plan(ids, experts, plan, place_of_pair, row_of_place):
+    T, top = ids.shape
+    flat = ids.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    place_of_pair[order] = torch.arange(T * top, dtype=torch.int32)
+    row_of_place[: T * top] = (order // top).to(torch.int32)
+    counts = torch.bincount(flat, minlength=experts)
+    plan[:experts] = (torch.cumsum(counts, 0) - counts).to(torch.int32)
+    plan[experts] = T * top
+    plan[experts + 1] = -1                      # no tiles: the plain statement of the grouped product reads the runs
+
+
+def moe_gemm(x, rows, w, out, plan, experts):
+    pairs = out.shape[0]
+    bounds = plan[: experts + 1].tolist()
+    for e in range(experts):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi > lo:
+            src = x[rows[lo:hi].long()] if rows is not None else x[lo:hi]
+            out[lo:hi] = (src.to(F32) @ w[e].to(F32).t()).to(out.dtype)
+
+
+def moe_combine(y, place_of_pair, weights, shared, gate, out):
+    T, top = weights.shape
+    acc = (weights[:, :, None] * y[place_of_pair[: T * top].long()].to(F32).view(T, top, -1)).sum(1)
+    if shared is not None:
+        acc = acc + (torch.sigmoid(gate)[:, None] if gate is not None else 1.0) * shared.to(F32)
+    out.copy_(acc.to(out.dtype))
+
+
 ALL = ("rotary_angles", "embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample",
-       "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out")
+       "act_mul", "gemm_act_mul", "attention_prep_row", "head_gate", "weighted_sum", "logit_cap", "gla_decay", "gla_scan", "gla_out",
+       "dyt_norm", "gemm_heads", "latent_prep", "latent_attention", "decay_scan", "mlstm_gates", "mlstm_out", "ssm_gates", "conv_silu",
+       "gated_group_norm", "moe_select", "moe_plan_size", "moe_plan", "moe_gemm", "moe_combine")
