@@ -183,8 +183,10 @@ def forward(config, W, tokens, rnd=_ident, layers_out=None):
         return rnd(dyn_tanh(v, W[name], W[name + ".b"], W[name + ".alpha"]))
 
     for i, layer in enumerate(config["layers"]):
-        src = layer.get("weights_of")
-        p = f"l{i if src is None else src}."
+        src = i
+        while config["layers"][src].get("weights_of") is not None:      # a layer may name a layer that itself names another
+            src = config["layers"][src]["weights_of"]
+        p = f"l{src}."
         x = x + rnd(MIXERS[layer["type"]](norm(p + "norm1", x), W, p + "mix.", layer["mixer"], eps, rnd))
         mlp = layer.get("mlp")
         if mlp is not None:
@@ -193,3 +195,10 @@ def forward(config, W, tokens, rnd=_ident, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return lin(W["head"], norm("final.norm", x)) * float(config["logit_scale"])
+
+
+def generate_greedy(config, W, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(torch.argmax(forward(config, W, toks)[-1])))
+    return toks[len(prompt):]
