@@ -98,12 +98,13 @@ def test_latent_attention_kernels(dtype, H, dn, dr, rdims, rank, window, ps):
     g = torch.Generator().manual_seed(H * 7 + rank)
     kd = rank + dr
     starts, lens = [37, 150, 0], [23, 1, 41]
-    T, pages = sum(lens), 40
+    T = sum(lens)
     width = H * (dn + dr) + 3
     q, dkv = torch.randn(T, width, generator=g).to(dtype), torch.randn(T, kd + 5, generator=g).to(dtype)
     cw = torch.rand(rank, generator=g) + 0.5
     inv = (10000.0 ** (-2.0 * torch.arange(rdims // 2, dtype=torch.float64) / max(rdims, 1))).float()
     need = [-(-(s + n) // ps) for s, n in zip(starts, lens)]
+    pages = sum(need) + 5
     perm = torch.randperm(pages, generator=g)[: sum(need)].to(torch.int32)
     bt = torch.full((3, max(need)), -1, dtype=torch.int32)
     at = 0
@@ -322,19 +323,21 @@ def _scale(t, name, f):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-def test_keys_at_the_windows_edges_decide_the_logits(dtype, tmp_path):
-    """Random weights make attention nearly uniform, which hides a window that is one token off.  Here the query matrices
-    are scaled up so that the softmax picks single keys; with windows of 6 and 13 the picked key often is the oldest visible
-    one.  The plain model with either window one longer or one shorter is far from the plain model (so the test would show
-    such a fault), and the engine is not, in prompts cut at every kind of place and in decoding."""
+@pytest.mark.parametrize("which,q_scale,o_scale", [(0, 14.0, 1.0), (1, 24.0, 6.0)])
+def test_keys_at_the_windows_edges_decide_the_logits(which, q_scale, o_scale, dtype, tmp_path):
+    """Random weights make attention nearly uniform, which hides a window that is one token off.  Here one layer's query
+    matrix is scaled up so that its softmax picks single keys (windows of 6 and 13: the picked key is the oldest visible one
+    every few positions).  The plain model with that window one longer or one shorter is far from the plain model at several
+    positions, so such a fault would show; the engine is not, in prompts cut at every kind of place and in decoding."""
     def change(t):
-        _scale(t, "l0.mix.q", 14.0), _scale(t, "l1.mix.q", 14.0)
+        _scale(t, f"l{which}.mix.q", q_scale), _scale(t, f"l{which}.mix.o", o_scale)
     d, cfg, w, toks, want, rc = _changed("L", tmp_path, change, 90)
-    for layer_, delta in ((0, 1), (0, -1), (1, 1), (1, -1)):
+    tol = max(REL[dtype] * float(want.std()), 4.5 * rc if dtype == torch.bfloat16 else 0.0)
+    for delta in (1, -1):
         off = copy.deepcopy(cfg)
-        off["layers"][layer_]["mixer"]["mask"]["size"] += delta
+        off["layers"][which]["mixer"]["mask"]["size"] += delta
         wrong = (plain.forward(off, w, toks) - want).abs().max(dim=-1).values
-        assert (wrong > 50 * REL[dtype] * float(want.std())).sum() > 10, "a window that is one off would not show"
+        assert (wrong > 3 * tol).sum() >= 2, "a window that is one off would not show"
     for sizes in ((90,), (40, 1, 1, 5, 2, 13, 6, 7) + (1,) * 15, (2,) * 10 + (3, 4, 12, 13, 14) + (1,) * 24):
         assert_close(_run_cut(d, dtype, PAGE_SIZES["L"], toks, sizes), want, dtype, f"cut {sizes[:4]}", rc)
 
@@ -411,7 +414,9 @@ def test_greedy_generation_equals_plain_model_f32(name, graph, tmp_path):
 
 
 def test_greedy_generation_bf16_stays_on_the_plain_models_best(tmp_path):
-    d = make_model_dir("Z3", seed=3, root=str(tmp_path), sigma=0.1)
+    """bfloat16 through the engine with CUDA graphs: every generated token is, for the plain model, the best token or within
+    what rounding costs of it; and a captured step gives the tokens the same step gives when it is launched kernel by kernel."""
+    d = make_model_dir("S", seed=3, root=str(tmp_path), sigma=0.2)
     cfg, w = read_model(d)
     prompts = [traces.make_requests(cfg["vocab"], [n], seed=n)["r0"] for n in (40, 3, 90, 9, 77)]
     eng = Engine(d, dtype="bfloat16", device=DEV, page_size=16, num_pages=40, num_slots=4)
@@ -420,8 +425,17 @@ def test_greedy_generation_bf16_stays_on_the_plain_models_best(tmp_path):
     for p, o in zip(prompts, outs):
         toks = list(p) + o.token_ids
         lg = plain.forward(cfg, w, toks[:-1])
+        slack = max(0.06 * float(lg.std()), 3 * rounding_cost(cfg, w, toks[:-1], lg))
         for i in range(len(p) - 1, len(toks) - 1):
-            assert lg[i][toks[i + 1]] >= lg[i].max() - 0.06 * float(lg.std()), (len(p), i)
+            assert lg[i][toks[i + 1]] >= lg[i].max() - slack, (len(p), i)
+    d = make_model_dir("Z3", seed=3, root=str(tmp_path))
+    prompts = [traces.make_requests(512, [n], seed=n)["r0"] for n in (40, 3, 90, 9)]
+    tokens = []
+    for graph in (True, False):
+        eng = Engine(d, dtype="bfloat16", device=DEV, page_size=16, num_pages=40, num_slots=4, cuda_graph=graph)
+        tokens.append([o.token_ids for o in eng.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))])
+        assert (eng.runner.graph_steps > 0) == graph
+    assert tokens[0] == tokens[1]
 
 
 # ------------------------------------------------------------------ the tools
