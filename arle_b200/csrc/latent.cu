@@ -15,7 +15,15 @@
 //    runs online per head in float32, then lane d accumulates output elements d, d + 32, ...  Tiles are counted
 //    from the first visible key max(0, p - window + 1), so the order of every sum depends on (first key, p)
 //    alone: a token's result is the same however the prompt was cut and whatever else is in the batch.
+//  * latent_attention_mma (bfloat16, rank 64 / 128 / 256 / 512, rotated part a multiple of 16): the same attention on the
+//    tensor cores.  Since every head reads the same records, the heads of a token are the rows of the products: a block
+//    takes one token, sixteen heads and a share of its keys; a tile of 64 records comes in by cp.async; Q . K^T (16 x 64,
+//    the four warps a quarter of the keys each) and P . V (16 x rank, the warps a quarter of the columns each, V being the
+//    record's first `rank` columns of the same tile) are mma.sync with float32 sums, the softmax in float32 between them.
+//    With few tokens in the step (decoding) a token's keys are shared out among several blocks whose parts
+//    latent_merge adds up, so that the machine is filled.
 #include "common.cuh"
+#include "mma_utils.cuh"
 using namespace arle;
 
 template <typename T>
@@ -190,6 +198,227 @@ static int launch_latent(const void* q_abs, void* out, const void* cache, const 
   launch_kernel(latent_attention_kernel<T, HPW>, dim3(grid), dim3(warps * 32), smem, s, 1, (const T*)q_abs, (T*)out, (const T*)cache,
                 positions, row_of_token, block_table, bt_stride, H, rank, kd, page_size, scale, window);
   return launch_status();
+}
+
+constexpr int kMmaTile = 64, kPPitch = 72;
+
+template <int R64>
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+    const __nv_bfloat16* __restrict__ q_abs, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ positions, const int* __restrict__ row_of_token,
+    const int* __restrict__ block_table, int bt_stride, int H, int kd, int page_size, float scale, int window, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int rank = 64 * R64;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int pitch = kd + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);          // [16][pitch]
+  __nv_bfloat16* Ks = Qs + 16 * pitch;                                  // [64][pitch]
+  __nv_bfloat16* Ps = Ks + kMmaTile * pitch;                            // [16][72]
+  float* red = reinterpret_cast<float*>(Ps + 16 * kPPitch);             // [4][16]
+  const int t = blockIdx.x, h0 = blockIdx.y * 16, sp = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)row_of_token[t] * bt_stride;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int ntiles = (pos - lo) / kMmaTile + 1;
+  const int tps = (ntiles + splits - 1) / splits;
+  const int tile_beg = sp * tps, tile_end = min(ntiles, tile_beg + tps);
+  const int chunks = kd >> 3;
+
+  for (int idx = tid; idx < 16 * chunks; idx += 128) {
+    const int r = idx / chunks, c = (idx - r * chunks) * 8;
+    if (h0 + r < H)
+      cp_async16(smem_u32(Qs + r * pitch + c), q_abs + ((size_t)t * H + h0 + r) * kd + c, 16);
+    else
+      *reinterpret_cast<uint4*>(Qs + r * pitch + c) = make_uint4(0, 0, 0, 0);
+  }
+  float o[2 * R64][4];
+#pragma unroll
+  for (int i = 0; i < 2 * R64; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int cbase = warp * 16 * R64;
+
+  for (int tile = tile_beg; tile < tile_end; ++tile) {
+    const int j0 = lo + tile * kMmaTile;
+    for (int idx = tid; idx < kMmaTile * chunks; idx += 128) {
+      const int r = idx / chunks, c = (idx - r * chunks) * 8;
+      const int j = j0 + r;
+      const bool ok = j <= pos;
+      const __nv_bfloat16* src = ok ? cache + ((size_t)bt[j / page_size] * page_size + j % page_size) * kd + c : cache;
+      cp_async16(smem_u32(Ks + r * pitch + c), src, ok ? 16 : 0);
+    }
+    cp_commit();
+    cp_wait<0>();
+    __syncthreads();
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int kk = 0; kk < (kd >> 4); ++kk) {
+      uint32_t a[4], b0, b1, b2, b3;
+      ldsm_x4(smem_u32(Qs + (lane & 15) * pitch + kk * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+      ldsm_x4(smem_u32(Ks + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+      mma_bf16(s[0], a, b0, b1);
+      mma_bf16(s[1], a, b2, b3);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = j0 + warp * 16 + n * 8 + 2 * t4 + (i & 1);
+        s[n][i] = j <= pos ? s[n][i] * scale : -INFINITY;
+      }
+    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (t4 == 0) {
+      red[warp * 16 + g] = mx0;
+      red[warp * 16 + g + 8] = mx1;
+    }
+    __syncthreads();
+    const float mn0 = fmaxf(m0, fmaxf(fmaxf(red[g], red[16 + g]), fmaxf(red[32 + g], red[48 + g])));
+    const float mn1 = fmaxf(m1, fmaxf(fmaxf(red[g + 8], red[24 + g]), fmaxf(red[40 + g], red[56 + g])));
+    const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);        // the tile's first key is visible, so mn is finite
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const float p0 = expf(s[n][0] - mn0), p1 = expf(s[n][1] - mn0), p2 = expf(s[n][2] - mn1), p3 = expf(s[n][3] - mn1);
+      ps0 += p0 + p1;
+      ps1 += p2 + p3;
+      const int col = warp * 16 + n * 8 + 2 * t4;
+      *reinterpret_cast<uint32_t*>(Ps + g * kPPitch + col) = pack_bf16(p0, p1);
+      *reinterpret_cast<uint32_t*>(Ps + (g + 8) * kPPitch + col) = pack_bf16(p2, p3);
+    }
+    l0 = l0 * c0 + ps0;
+    l1 = l1 * c1 + ps1;
+    m0 = mn0;
+    m1 = mn1;
+#pragma unroll
+    for (int i = 0; i < 2 * R64; ++i) {
+      o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMmaTile / 16; ++kk) {
+      uint32_t pa[4];
+      ldsm_x4(smem_u32(Ps + (lane & 15) * kPPitch + kk * 16 + (lane >> 4) * 8), pa[0], pa[1], pa[2], pa[3]);
+#pragma unroll
+      for (int dn = 0; dn < R64; ++dn) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(Ks + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + cbase + dn * 16 + (lane >> 4) * 8), b0, b1, b2, b3);
+        mma_bf16(o[2 * dn], pa, b0, b1);
+        mma_bf16(o[2 * dn + 1], pa, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  if (tile_beg >= tile_end) {
+    cp_commit();
+    cp_wait<0>();
+  }
+  // the rows' sums: over the four lanes of a row, then over the warps (each saw a quarter of every tile's keys)
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();
+  if (t4 == 0) {
+    red[warp * 16 + g] = l0;
+    red[warp * 16 + g + 8] = l1;
+  }
+  __syncthreads();
+  const float lt0 = red[g] + red[16 + g] + red[32 + g] + red[48 + g];
+  const float lt1 = red[g + 8] + red[24 + g] + red[40 + g] + red[56 + g];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int h = h0 + g + half * 8;
+    if (h >= H) continue;
+    const float lt = half ? lt1 : lt0;
+    if (splits == 1) {
+      const float inv = 1.0f / lt;
+      __nv_bfloat16* op = out + ((size_t)t * H + h) * rank + cbase + 2 * t4;
+#pragma unroll
+      for (int n = 0; n < 2 * R64; ++n)
+        *reinterpret_cast<uint32_t*>(op + n * 8) = pack_bf16(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+    } else {
+      const size_t slot = ((size_t)t * H + h) * splits + sp;
+      float* op = part_o + slot * rank + cbase + 2 * t4;
+#pragma unroll
+      for (int n = 0; n < 2 * R64; ++n) {
+        op[n * 8] = o[n][2 * half];
+        op[n * 8 + 1] = o[n][2 * half + 1];
+      }
+      if (warp == 0 && t4 == 0) {
+        part_ml[slot * 2] = half ? m1 : m0;
+        part_ml[slot * 2 + 1] = lt;
+      }
+    }
+  }
+}
+
+// The parts of a (token, head) that several blocks hold: out = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, s ascending.
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                                    int rank, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t th = blockIdx.x;
+  const float* ml = part_ml + th * splits * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s)
+    if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+  float den = 0.f;
+  for (int s = 0; s < splits; ++s)
+    if (ml[2 * s + 1] > 0.f) den += expf(ml[2 * s] - M) * ml[2 * s + 1];
+  const float inv = 1.0f / den;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s)
+      if (ml[2 * s + 1] > 0.f) acc = fmaf(expf(ml[2 * s] - M), part_o[(th * splits + s) * rank + c], acc);
+    out[th * rank + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int R64>
+static int launch_latent_mma(const void* q_abs, void* out, float* part_o, float* part_ml, const void* cache, const int* positions,
+                             const int* row_of_token, const int* block_table, int bt_stride, int H, int kd, int page_size, float scale,
+                             int window, int num_tokens, int splits, cudaStream_t s) {
+  const size_t smem = (size_t)(16 + kMmaTile) * (kd + 8) * 2 + 16 * kPPitch * 2 + 64 * sizeof(float);
+  if (smem > 220 * 1024) return ARLE_E_UNSUPPORTED;
+  cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<R64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(num_tokens, (H + 15) / 16, splits);
+  launch_kernel(latent_attention_mma_kernel<R64>, dim3(grid), dim3(128), smem, s, 1, (const __nv_bfloat16*)q_abs, (__nv_bfloat16*)out,
+                part_o, part_ml, (const __nv_bfloat16*)cache, positions, row_of_token, block_table, bt_stride, H, kd, page_size, scale,
+                window, splits);
+  if (splits > 1)
+    launch_kernel(latent_merge_kernel, dim3(num_tokens * H), dim3(64 * R64 >= 256 ? 128 : 64), 0, s, 1, (const float*)part_o,
+                  (const float*)part_ml, (__nv_bfloat16*)out, 64 * R64, splits);
+  return launch_status();
+}
+
+// The tensor-core form: bfloat16, rank 64 / 128 / 256 / 512, kd - rank a multiple of 16.  splits > 1 needs part_o float32
+// [T * H * splits * rank] and part_ml float32 [T * H * splits * 2].
+ARLE_API int arle_latent_attention_mma(const void* q_abs, void* out, float* part_o, float* part_ml, const void* cache,
+                                       const int* positions, const int* row_of_token, const int* block_table, int bt_stride, int H,
+                                       int rank, int kd, int page_size, float scale, int window, int num_tokens, int splits,
+                                       cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (H <= 0 || kd < rank || (kd - rank) % 16 || page_size <= 0 || splits < 1 || splits > 65535 || (H + 15) / 16 > 65535 ||
+      (splits > 1 && (!part_o || !part_ml)))
+    return ARLE_E_BADARG;
+#define ARLE_LAT(R) \
+  return launch_latent_mma<R>(q_abs, out, part_o, part_ml, cache, positions, row_of_token, block_table, bt_stride, H, kd, page_size, \
+                              scale, window, num_tokens, splits, s)
+  if (rank == 64) ARLE_LAT(1);
+  if (rank == 128) ARLE_LAT(2);
+  if (rank == 256) ARLE_LAT(4);
+  if (rank == 512) ARLE_LAT(8);
+#undef ARLE_LAT
+  return ARLE_E_UNSUPPORTED;
 }
 
 // q_abs [T, H, kd] (folded queries: rank columns, then the rotated part), out [T, H, rank], cache [pages, 1, page_size, kd].

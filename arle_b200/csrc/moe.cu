@@ -12,8 +12,13 @@
 //  * moe_gemm: C[place, :] = A[row(place), :] . W[expert(place)]^T in tiles of 64 x 64, float32 sums with k ascending
 //    (the per-expert twin of the plain product).  `rows` maps a place to its row of A (the token of the pair) or is
 //    absent (A is already in place order).
+//    In bfloat16 with aligned rows the same product runs on the tensor cores (moe_gemm_mma: tiles of 64 places x 128
+//    columns, mma.sync with float32 sums, operands brought in by cp.async in two stages), and a step of few pairs
+//    (decoding) runs it as one dot product a warp (moe_gemv: every chosen expert's rows are streamed once, 16 bytes
+//    a lane and load), since a tile of 64 places would be all but empty.
 //  * moe_combine: out[t] = sum_k weight[t, k] * Y[place(t, k)] (k ascending) + sigmoid(gate[t]) * shared[t].
 #include "common.cuh"
+#include "mma_utils.cuh"
 using namespace arle;
 
 __global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ correction,
@@ -197,13 +202,149 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
   }
 }
 
+constexpr int TM = 64, TN = 128, TK = 32, TPITCH = 40;
+
+__global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ rows,
+                                                           const __nv_bfloat16* __restrict__ W, int ldw, long w_expert,
+                                                           __nv_bfloat16* __restrict__ C, int ldc, const int* __restrict__ plan, int E,
+                                                           int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[E + 1]) return;
+  const int* tt = plan + E + 2 + 3 * tile;
+  const int expert = tt[0], p0 = tt[1], M = tt[2];
+  __shared__ __align__(16) __nv_bfloat16 As[2][TM * TPITCH];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2][TN * TPITCH];
+  __shared__ int arow[TM];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp & 1, wn = warp >> 1;
+  const int n0 = blockIdx.x * TN;
+  if (tid < TM) arow[tid] = tid < M ? (rows ? rows[p0 + tid] : p0 + tid) : -1;
+  __syncthreads();
+  W += (size_t)expert * w_expert;
+  auto load = [&](int stage, int k0) {
+    {
+      const int r = tid >> 2, c = (tid & 3) * 8;
+      const int ar = arow[r];
+      const bool ok = ar >= 0 && k0 + c < K;
+      cp_async16(smem_u32(&As[stage][r * TPITCH + c]), ok ? A + (size_t)ar * lda + k0 + c : A, ok ? 16 : 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int id = tid + i * 256;
+      const int r = id >> 2, c = (id & 3) * 8;
+      const bool ok = n0 + r < N && k0 + c < K;
+      cp_async16(smem_u32(&Ws[stage][r * TPITCH + c]), ok ? W + (size_t)(n0 + r) * ldw + k0 + c : W, ok ? 16 : 0);
+    }
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+  const int nk = (K + TK - 1) / TK;
+  load(0, 0);
+  cp_commit();
+  for (int kt = 0; kt < nk; ++kt) {
+    const int st = kt & 1;
+    if (kt + 1 < nk) {
+      load(st ^ 1, (kt + 1) * TK);
+      cp_commit();
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK / 16; ++kk) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldsm_x4(smem_u32(&As[st][(wm * 32 + mt * 16 + (lane & 15)) * TPITCH + kk * 16 + (lane >> 4) * 8]), a[mt][0], a[mt][1], a[mt][2],
+                a[mt][3]);
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_u32(&Ws[st][(wn * 32 + nb * 16 + (lane >> 4) * 8 + (lane & 7)) * TPITCH + kk * 16 + ((lane >> 3) & 1) * 8]), b0, b1,
+                b2, b3);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16(acc[mt][2 * nb], a[mt], b0, b1);
+          mma_bf16(acc[mt][2 * nb + 1], a[mt], b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int m = wm * 32 + mt * 16 + g + half * 8;
+        const int col = n0 + wn * 32 + nt * 8 + 2 * t4;
+        if (m >= M) continue;
+        __nv_bfloat16* cp = C + (size_t)(p0 + m) * ldc + col;
+        if (col < N) cp[0] = __float2bfloat16_rn(acc[mt][nt][2 * half]);
+        if (col + 1 < N) cp[1] = __float2bfloat16_rn(acc[mt][nt][2 * half + 1]);
+      }
+}
+
+// One warp per (place, output column): the dot product of the place's row of A with one row of its expert's matrix,
+// eight elements a lane and load (K a multiple of 8, rows on 16-byte boundaries).
+__global__ void __launch_bounds__(256) moe_gemv_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ rows,
+                                                       const __nv_bfloat16* __restrict__ W, int ldw, long w_expert,
+                                                       __nv_bfloat16* __restrict__ C, int ldc, const int* __restrict__ plan, int E, int N,
+                                                       int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int place = blockIdx.y;
+  if (place >= plan[E]) return;
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= N) return;
+  int expert = 0;
+  while (expert + 1 < E && plan[expert + 1] <= place) ++expert;
+  const __nv_bfloat16* a = A + (size_t)(rows ? rows[place] : place) * lda;
+  const __nv_bfloat16* w = W + (size_t)expert * w_expert + (size_t)n * ldw;
+  float acc = 0.f;
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 av = *reinterpret_cast<const uint4*>(a + k);
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc = fmaf(__low2float(a2[i]), __low2float(w2[i]), acc);
+      acc = fmaf(__high2float(a2[i]), __high2float(w2[i]), acc);
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) C[(size_t)place * ldc + n] = __float2bfloat16_rn(acc);
+}
+
 // dtype: type of A and C; w_dtype: type of W [E][N][K] (an expert every w_expert elements).  pairs: places in all.
+// fast: bfloat16 operands with aligned rows may take the tensor-core tiles or, for few pairs, the dot products.
 ARLE_API int arle_moe_gemm(const void* A, int lda, const int* rows, const void* W, int ldw, long w_expert, void* C, int ldc,
-                           int dtype, int w_dtype, const int* plan, int E, int pairs, int N, int K, cudaStream_t s) {
+                           int dtype, int w_dtype, const int* plan, int E, int pairs, int N, int K, int fast, cudaStream_t s) {
   if (pairs <= 0 || N <= 0) return 0;
   if (K <= 0 || E <= 0) return ARLE_E_BADARG;
   const int max_tiles = pairs / kMoeTile + E + 1;
   if (max_tiles > 65535) return ARLE_E_UNSUPPORTED;
+  if (fast && dtype == 1 && w_dtype == 1 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && w_expert % 8 == 0 &&
+      ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+    if (pairs <= 128) {
+      launch_kernel(moe_gemv_kernel, dim3((N + 7) / 8, pairs), dim3(256), 0, s, 1, (const __nv_bfloat16*)A, lda, rows,
+                    (const __nv_bfloat16*)W, ldw, w_expert, (__nv_bfloat16*)C, ldc, plan, E, N, K);
+    } else {
+      launch_kernel(moe_gemm_mma_kernel, dim3((N + TN - 1) / TN, max_tiles), dim3(256), 0, s, 1, (const __nv_bfloat16*)A, lda, rows,
+                    (const __nv_bfloat16*)W, ldw, w_expert, (__nv_bfloat16*)C, ldc, plan, E, N, K);
+    }
+    return launch_status();
+  }
   dim3 grid((N + GN - 1) / GN, max_tiles);
   if (dtype == 0 && w_dtype == 0)
     launch_kernel(moe_gemm_kernel<float, float, float>, dim3(grid), dim3(256), 0, s, 1, (const float*)A, lda, rows, (const float*)W, ldw,

@@ -77,6 +77,7 @@ _SIGNATURES = {
     "arle_dyt_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
     "arle_gemm_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
     "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_latent_attention": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "arle_decay_scan": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, ctypes.c_long, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "arle_mlstm_gates": [_P, _I, _P, _P, _F, _P, _P, _P, ctypes.c_long, ctypes.c_long, _P, _P, _P, _I, _I, _P],
@@ -86,7 +87,7 @@ _SIGNATURES = {
     "arle_gated_group_norm": [_P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P],
     "arle_moe_select": [_P, _I, _P, _P, _I, _I, _I, _I, _F, _P, _P, _I, _P],
     "arle_moe_plan": [_P, _I, _I, _I, _P, _P, _P, _P],
-    "arle_moe_gemm": [_P, _I, _P, _P, _I, ctypes.c_long, _P, _I, _I, _I, _P, _I, _I, _I, _I, _P],
+    "arle_moe_gemm": [_P, _I, _P, _P, _I, ctypes.c_long, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P],
     "arle_moe_combine": [_P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
 }
 
@@ -1082,10 +1083,21 @@ def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps: float, inv_freq,
                                       rank, T, _stream()), "latent_prep")
 
 
-def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank: int, page_size: int, scale: float, window) -> None:
+def latent_mma_supported(q_abs, rank: int) -> bool:
+    """The tensor-core latent attention takes bfloat16, a latent of 64, 128, 256 or 512 and a rotated part that is a multiple
+    of 16; everything else runs on the general kernel."""
+    kd = q_abs.shape[2]
+    return (_KERNEL_SET == "fast" and q_abs.dtype == torch.bfloat16 and rank in (64, 128, 256, 512) and (kd - rank) % 16 == 0
+            and q_abs.data_ptr() % 16 == 0)
+
+
+def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank: int, page_size: int, scale: float, window,
+                     batch=None) -> None:
     """Causal attention of folded queries q_abs [T, heads, kd] over records cache [pages, 1, page_size, kd]: head h's score
     against record j is (q_abs[t, h] . record_j) * scale, its output sum_j softmax_j * record_j[:rank] (out [T, heads,
-    rank]).  ``window`` None or <= 0: all keys; W: keys p - W + 1 .. p.  float32 arithmetic."""
+    rank]).  ``window`` None or <= 0: all keys; W: keys p - W + 1 .. p.  Scores, softmax and sums are float32.  ``batch`` (a
+    StepContext, for its scratch buffers) lets the tensor-core kernel run where the shapes allow it; with few tokens in
+    the step a token's keys are shared out among several blocks."""
     T, heads, kd = q_abs.shape
     if (not q_abs.is_contiguous() or tuple(out.shape) != (T, heads, rank) or not out.is_contiguous() or out.dtype != q_abs.dtype
             or cache.dtype != q_abs.dtype or tuple(cache.shape[1:]) != (1, page_size, kd) or not cache.is_contiguous()):
@@ -1093,6 +1105,23 @@ def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, ra
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("latent_attention: block table rows must be contiguous")
+    if batch is not None and latent_mma_supported(q_abs, rank):
+        bound = block_table.shape[1] * page_size
+        if window:
+            bound = min(bound, int(window) + 63)
+        blocks = T * (-(-heads // 16))
+        splits = max(1, min(-(-bound // 64), -(-4 * sm_count(q_abs.device) // blocks), 64))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = batch.ws.get("latent_part_o", (T * heads * splits * rank,), torch.float32)
+            part_ml = batch.ws.get("latent_part_ml", (T * heads * splits * 2,), torch.float32)
+        _check(library().arle_latent_attention_mma(_ptr(q_abs), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(cache), _ptr(positions),
+                                                   _ptr(row_of_token), _ptr(block_table), block_table.stride(0), heads, rank, kd,
+                                                   page_size, float(scale), int(window) if window else 0, T, splits, _stream()),
+               "latent_attention_mma")
+        if splits > 1:
+            add_launches(1)
+        return
     _check(library().arle_latent_attention(_ptr(q_abs), _ptr(out), _ptr(cache), _dt(q_abs), _ptr(positions), _ptr(row_of_token),
                                            _ptr(block_table), block_table.stride(0), heads, rank, kd, page_size, float(scale),
                                            int(window) if window else 0, T, _stream()), "latent_attention")
@@ -1273,7 +1302,9 @@ def moe_plan(ids, experts: int, plan, place_of_pair, row_of_place) -> None:
 
 def moe_gemm(x, rows, w, out, plan, experts: int) -> None:
     """out[place] = x[rows[place]] . w[expert of place]^T for every place of the plan (rows None: x is in place order).
-    x [*, K], w [experts, N, K] contiguous, out [pairs, N] in x's type; float32 sums, k ascending."""
+    x [*, K], w [experts, N, K] contiguous, out [pairs, N] in x's type; float32 sums, k ascending.  With the fast kernel
+    set, bfloat16 operands with rows on 16-byte boundaries run on the tensor cores (many pairs) or as one dot product a
+    warp (up to 128 pairs: a decode step)."""
     pairs, N = out.shape
     K = x.shape[1]
     if (w.dim() != 3 or w.shape[0] != experts or w.shape[1] != N or w.shape[2] != K or not w.is_contiguous() or x.stride(1) != 1
@@ -1281,7 +1312,7 @@ def moe_gemm(x, rows, w, out, plan, experts: int) -> None:
         raise KernelError(f"moe_gemm: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     _i32(rows, "rows"), _i32(plan, "plan")
     _check(library().arle_moe_gemm(_ptr(x), x.stride(0), _ptr(rows), _ptr(w), K, N * K, _ptr(out), out.stride(0), _dt(x), _dt(w),
-                                   _ptr(plan), experts, pairs, N, K, _stream()), "moe_gemm")
+                                   _ptr(plan), experts, pairs, N, K, int(_KERNEL_SET == "fast"), _stream()), "moe_gemm")
 
 
 def moe_combine(y, place_of_pair, weights, shared, gate, out) -> None:

@@ -130,7 +130,7 @@ class LatentAttention(Mixer):
             q_abs[:, :, :rank].zero_()
         o_lat = ctx.ws.get("latent_o", (T, H, rank), x.dtype)
         ops.latent_attention(q_abs, o_lat, records, ctx.positions, ctx.row_of_token, cache.block_table, rank, cache.page_size,
-                             s.scale, s.window)
+                             s.scale, s.window, batch=ctx)
         heads_out = ctx.ws.get("attn_out", (T, H, s.value_dim), x.dtype)
         ops.gemm_heads(o_lat, self.w_uv, heads_out)
         out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)

@@ -17,6 +17,8 @@ single-GPU one: for --gpus above 1 it says so and exits with 2.
 
 ``--design kolodra`` leaves the default workload alone and prints another record: a few Kolodra layers
 beside as many Qwen3 layers of equal sizes, prefill and decode, with every kernel's time per layer.
+``--design zuderax`` does the same for Zuderax layers (a latent attention, a matrix LSTM and a Mamba-2 layer in turn,
+every second feed-forward one of routed experts) beside Kolodra and Qwen3 layers of equal width.
 """
 import argparse
 import json
@@ -155,6 +157,27 @@ DESIGN_SIZES = {"0.6b": dict(width=1024, ff=3072, heads=16, kv=8, hd=128, rheads
                 "8b": dict(width=4096, ff=12288, heads=32, kv=8, hd=128, rheads=16, rank=64, vocab=32768)}
 
 
+# Mixer sizes for ``--design zuderax`` at the same widths: a latent of a quarter / an eighth of the width, a window of half
+# the benchmark's context, recurrent states of 64 x 128 / 256 x 512 (matrix LSTM) and 128 x 64 (Mamba-2, inner = 2 x width),
+# experts whose chosen ones together are as wide as the dense feed-forward.
+ZUDERAX_SIZES = {"0.6b": dict(heads=16, dim=64, rot=32, vdim=64, rank=256, lstm=(8, 64, 128), ssm=(32, 64, 128, 1), experts=16, top=4, groups=4,
+                              keep=2),
+                 "8b": dict(heads=32, dim=128, rot=64, vdim=128, rank=512, lstm=(8, 256, 512), ssm=(128, 64, 128, 8), experts=32, top=4, groups=4,
+                            keep=2)}
+
+
+def zuderax_config(z, zz, L, window):
+    ff = {"kind": "dense", "ff": z["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // zz["top"]}, "shared": {"ff": z["ff"] // zz["top"]},
+              "router": {"experts": zz["experts"], "top": zz["top"], "scale": 2.5, "groups": {"count": zz["groups"], "keep": zz["keep"]}}}
+    mixers = [("latent_attention", {"heads": zz["heads"], "dim": zz["dim"], "rot_dim": zz["rot"], "vdim": zz["vdim"], "kv_rank": zz["rank"],
+                                    "scale": (zz["dim"] + zz["rot"]) ** -0.5, "mask": {"size": window}, "rot": {"base": 1e6, "dims": zz["rot"]}}),
+              ("mlstm", {"heads": zz["lstm"][0], "dim": zz["lstm"][1], "vdim": zz["lstm"][2], "gate_cap": 15.0}),
+              ("mamba2", {"heads": zz["ssm"][0], "vdim": zz["ssm"][1], "state": zz["ssm"][2], "groups": zz["ssm"][3], "conv": 4, "norm_groups": 1})]
+    layers = [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1], "mlp": routed if i % 2 else ff} for i in range(L)]
+    return {"architecture": "Zuderax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
+
+
 def design_table(args, torch, ops, pk) -> int:
     """``--design kolodra``: prefill and decode throughput of a few Kolodra layers beside the same number of Qwen3
     layers of equal width, heads and feed-forward, with the device time of every kernel of one step (profiler
@@ -164,9 +187,9 @@ def design_table(args, torch, ops, pk) -> int:
     from arle_b200.engine import ModelRunner, StepEntry, random_model
 
     dev = torch.device("cuda:0")
-    L, T, C = args.layers or 4, args.prefill_tokens, args.context
+    L, T, C = args.layers or (6 if args.design == "zuderax" else 4), args.prefill_tokens, args.context
     gen = torch.Generator().manual_seed(1)
-    out = {"design": "kolodra", "layers": L, "prefill_tokens": T, "context": C, "dtype": "bf16", "peaks": pk, "sizes": {}}
+    out = {"design": args.design, "layers": L, "prefill_tokens": T, "context": C, "dtype": "bf16", "peaks": pk, "sizes": {}}
 
     def kolodra_config(z):
         layer = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["ff"]},
@@ -262,7 +285,12 @@ def design_table(args, torch, ops, pk) -> int:
 
     for name in ([args.sizes] if args.sizes in DESIGN_SIZES and args.sizes != "8b" else list(DESIGN_SIZES)):
         z = DESIGN_SIZES[name]
-        out["sizes"][name] = {"config": z, "kolodra": measure(kolodra_config(z)), "qwen3": measure(qwen_config(z))}
+        out["sizes"][name] = {"config": z}
+        if args.design == "zuderax":
+            out["sizes"][name]["mixers"] = ZUDERAX_SIZES[name]
+            out["sizes"][name]["zuderax"] = measure(zuderax_config(z, ZUDERAX_SIZES[name], L, max(C // 2, 16)))
+        if not args.design_alone:
+            out["sizes"][name].update({"kolodra": measure(kolodra_config(z)), "qwen3": measure(qwen_config(z))})
     print(json.dumps(out))
     return 0
 
@@ -289,7 +317,8 @@ def main() -> int:
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-kernel-times", action="store_true",
                     help="with --design: leave out the per-kernel times (they come from torch's profiler, which cannot run under another profiler)")
-    ap.add_argument("--design", default=None, choices=["kolodra"],
+    ap.add_argument("--design-alone", action="store_true", help="with --design zuderax: leave out the models it stands beside")
+    ap.add_argument("--design", default=None, choices=["kolodra", "zuderax"],
                     help="instead of the default workload: a few layers of this design beside as many Qwen3 layers of equal "
                          "sizes, prefill and decode, with every kernel's time (uses --layers, --steps, --context, --prefill-tokens)")
     ap.add_argument("--timeline", action="store_true",

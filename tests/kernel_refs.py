@@ -298,7 +298,7 @@ def latent_prep(q, dkv, positions, slot_mapping, c_weight, eps, inv_freq, rot_di
     q_abs[:, :, rank:] = _turn_half(qr, positions, inv_freq, rot_dims).to(q_abs.dtype)
 
 
-def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank, page_size, scale, window):
+def latent_attention(q_abs, out, cache, positions, row_of_token, block_table, rank, page_size, scale, window, batch=None):
     T, H, kd = q_abs.shape
     for t in range(T):
         p = int(positions[t])

@@ -92,12 +92,15 @@ def test_dyn_tanh_kernel(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,dn,dr,rdims,rank,window,ps", [(3, 16, 8, 8, 20, 7, 4), (1, 8, 16, 12, 33, 0, 8), (16, 64, 32, 32, 128, 48, 16),
-                                                          (5, 24, 6, 0, 70, 1, 16), (12, 8, 64, 64, 512, 100, 32)])
+                                                          (5, 24, 6, 0, 70, 1, 16), (12, 8, 64, 64, 512, 100, 32), (4, 16, 16, 16, 64, 0, 16),
+                                                          (40, 32, 16, 16, 256, 300, 16), (20, 8, 0, 0, 128, 129, 8)])
 def test_latent_attention_kernels(dtype, H, dn, dr, rdims, rank, window, ps):
-    """Three rows of unequal length in scattered pages: a portion that continues a request, a decoded token, a fresh prompt."""
+    """Three rows of unequal length in scattered pages: a portion that continues a request, a decoded token far into its
+    request, a fresh prompt.  Where the tensor-core kernel takes the shapes it is compared with the same plain statement,
+    with the step as it is (a token's keys in few parts) and with the decoded token alone (its keys in many parts)."""
     g = torch.Generator().manual_seed(H * 7 + rank)
     kd = rank + dr
-    starts, lens = [37, 150, 0], [23, 1, 41]
+    starts, lens = [37, 700, 0], [23, 1, 41]
     T = sum(lens)
     width = H * (dn + dr) + 3
     q, dkv = torch.randn(T, width, generator=g).to(dtype), torch.randn(T, kd + 5, generator=g).to(dtype)
@@ -125,8 +128,24 @@ def test_latent_attention_kernels(dtype, H, dn, dr, rdims, rank, window, ps):
         torch.testing.assert_close(a, c, **_tol(dtype))
     q_abs = torch.cat([c.to(dtype), qc.to(dtype)[:, :, rank:]], dim=-1).contiguous()
     out = torch.zeros(T, H, rank, dtype=dtype)
-    for (a, c) in _both("latent_attention", [q_abs, out, cc.to(dtype), pos, row, bt, rank, ps, 0.4 * kd ** -0.5, window or None], [1]):
+    args = [q_abs, out, cc.to(dtype), pos, row, bt, rank, ps, 0.4 * kd ** -0.5, window or None]
+    for (a, c) in _both("latent_attention", args, [1]):
         torch.testing.assert_close(a, c, **_tol(dtype))
+    if ops.latent_mma_supported(q_abs.to(DEV), rank):
+        from types import SimpleNamespace
+
+        from arle_b200.engine.batch import Workspace
+        batch = SimpleNamespace(ws=Workspace(DEV))
+        dev = [x.to(DEV) if isinstance(x, torch.Tensor) else x for x in args]
+        before = ops.launch_count()
+        ops.latent_attention(*dev, batch=batch)
+        torch.testing.assert_close(dev[1].float().cpu(), c, **_tol(dtype))
+        one = slice(lens[0], lens[0] + 1)                               # the decoded token alone: a step of one row
+        got = torch.zeros(1, H, rank, dtype=dtype, device=DEV)
+        ops.latent_attention(dev[0][one].contiguous(), got, dev[2], dev[3][one].contiguous(), torch.zeros(1, dtype=torch.int32, device=DEV),
+                             dev[5][1:2].contiguous(), rank, ps, args[8], args[9], batch=batch)
+        torch.testing.assert_close(got.float().cpu(), c[one], **_tol(dtype))
+        assert ops.launch_count() - before == 4                          # both ran in parts and were merged
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
