@@ -11,8 +11,8 @@
 //
 //  * decay_scan: a block per (row of the step, head, tile of columns).  A column of S (dim numbers, stored
 //    contiguously: the state is kept transposed, [head][column][dim]) is held by `lpc` lanes, EPL numbers a lane;
-//    the lanes add their parts of o_t by shuffles.  q, k, v, a, b of 16 tokens are staged in shared memory, then
-//    the 16 steps run from there.  The split of a column depends on dim alone, so a token's sums have one order
+//    the lanes add their parts of o_t by shuffles; a thread holds one column, or four that share its loads of k and q.
+//    q, k, b v and a of 16 tokens are staged in shared memory, then the 16 steps run from there.  The split of a column depends on dim alone, so a token's sums have one order
 //    whatever the cutting or the batch.
 //  * mlstm_gates: the log gates of the matrix LSTM (soft-capped), its running maximum m (carried in the state),
 //    and from them a_t, b_t and exp(-m_t); the gates of 128 tokens are evaluated side by side, the maximum runs
@@ -30,7 +30,7 @@ using namespace arle;
 constexpr int kScanChunk = 16;
 constexpr int kScanThreads = 256;
 
-template <typename T, int EPL>
+template <typename T, int EPL, int CPT>
 __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int q_stride, int k_stride, int v_stride,
     const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ state, long slot_stride,
@@ -38,86 +38,121 @@ __global__ void __launch_bounds__(kScanThreads) decay_scan_kernel(
     int dim, int vdim, int ones_col, float q_scale, int lpc) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
-  const int cpb = kScanThreads / lpc;                    // columns of S a block holds
-  float* qs = sm;                                        // [chunk][dim]
-  float* ksm = qs + kScanChunk * dim;                    // [chunk][dim]
-  float* vs = ksm + kScanChunk * dim;                    // [chunk][cpb]
+  extern __shared__ __align__(16) float sm[];
+  const int cpb = kScanThreads / lpc * CPT;              // columns of S a block holds: CPT to a thread
+  const int dpad = lpc * EPL;                            // a token's q or k in shared memory, padded with zeros to the lanes' shares
+  float* qs = sm;                                        // [chunk][dpad]
+  float* ksm = qs + kScanChunk * dpad;                   // [chunk][dpad]
+  float* vs = ksm + kScanChunk * dpad;                   // [chunk][cpb], already times b
   float* as = vs + kScanChunk * cpb;                     // [chunk]
-  float* bs = as + kScanChunk;                           // [chunk]
   const int r = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * cpb;
   const int vcols = vdim + ones_col;
   const int g = h / (H / kq_heads);
-  const int col_local = threadIdx.x / lpc, part = threadIdx.x % lpc;
-  const int col = c0 + col_local;
-  const bool active = col < vcols;
+  const int cl0 = threadIdx.x / lpc * CPT, part = threadIdx.x % lpc;      // the thread's first column inside the block
   const int e0 = part * EPL;
   const int beg = q_indptr[r], end = q_indptr[r + 1];
-  float* sp = state + (size_t)state_slots[r] * slot_stride + ((size_t)h * vcols + (active ? col : 0)) * dim;
-  float S[EPL];
+  float* sp = state + (size_t)state_slots[r] * slot_stride + (size_t)h * vcols * dim;
+  float S[CPT][EPL];
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) S[i] = (active && e0 + i < dim) ? sp[e0 + i] : 0.f;
+  for (int j = 0; j < CPT; ++j)
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) S[j][i] = (c0 + cl0 + j < vcols && e0 + i < dim) ? sp[(size_t)(c0 + cl0 + j) * dim + e0 + i] : 0.f;
 
   for (int t0 = beg; t0 < end; t0 += kScanChunk) {
     const int n = min(kScanChunk, end - t0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * dim; idx += kScanThreads) {
-      const int tt = idx / dim, e = idx - tt * dim;
-      qs[idx] = to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) * q_scale;
-      ksm[idx] = to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]);
+    for (int idx = threadIdx.x; idx < n * dpad; idx += kScanThreads) {
+      const int tt = idx / dpad, e = idx - tt * dpad;
+      const bool in = e < dim;
+      qs[idx] = in ? to_f32(q[(size_t)(t0 + tt) * q_stride + (size_t)g * dim + e]) * q_scale : 0.f;
+      ksm[idx] = in ? to_f32(k[(size_t)(t0 + tt) * k_stride + (size_t)g * dim + e]) : 0.f;
     }
     for (int idx = threadIdx.x; idx < n * cpb; idx += kScanThreads) {
       const int tt = idx / cpb, cc = idx - tt * cpb;
       const int c = c0 + cc;
-      vs[idx] = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
+      const float vv = c < vdim ? to_f32(v[(size_t)(t0 + tt) * v_stride + (size_t)h * vdim + c]) : (c == vdim && ones_col ? 1.f : 0.f);
+      vs[idx] = b[(size_t)(t0 + tt) * H + h] * vv;
     }
-    if (threadIdx.x < n) {
-      as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * H + h];
-      bs[threadIdx.x] = b[(size_t)(t0 + threadIdx.x) * H + h];
-    }
+    if (threadIdx.x < n) as[threadIdx.x] = a[(size_t)(t0 + threadIdx.x) * H + h];
     __syncthreads();
     for (int tt = 0; tt < n; ++tt) {
       const float at = as[tt];
-      const float bv = bs[tt] * vs[tt * cpb + col_local];
-      const float* kt = ksm + tt * dim + e0;
-      const float* qt = qs + tt * dim + e0;
-      float p = 0.f;
+      float bv[CPT], p[CPT];
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        if (e0 + i < dim) {
-          S[i] = fmaf(at, S[i], bv * kt[i]);
-          p = fmaf(S[i], qt[i], p);
+      for (int j = 0; j < CPT; ++j) {
+        bv[j] = vs[tt * cpb + cl0 + j];
+        p[j] = 0.f;
+      }
+      const float4* kt = reinterpret_cast<const float4*>(ksm + tt * dpad + e0);
+      const float4* qt = reinterpret_cast<const float4*>(qs + tt * dpad + e0);
+#pragma unroll
+      for (int i = 0; i < EPL / 4; ++i) {
+        const float4 kv = kt[i], qv = qt[i];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+          S[j][4 * i] = fmaf(at, S[j][4 * i], bv[j] * kv.x);
+          p[j] = fmaf(S[j][4 * i], qv.x, p[j]);
+          S[j][4 * i + 1] = fmaf(at, S[j][4 * i + 1], bv[j] * kv.y);
+          p[j] = fmaf(S[j][4 * i + 1], qv.y, p[j]);
+          S[j][4 * i + 2] = fmaf(at, S[j][4 * i + 2], bv[j] * kv.z);
+          p[j] = fmaf(S[j][4 * i + 2], qv.z, p[j]);
+          S[j][4 * i + 3] = fmaf(at, S[j][4 * i + 3], bv[j] * kv.w);
+          p[j] = fmaf(S[j][4 * i + 3], qv.w, p[j]);
         }
       }
-      for (int o = lpc >> 1; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-      if (part == 0 && active) out[((size_t)(t0 + tt) * H + h) * vcols + col] = p;
+      for (int o = lpc >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) p[j] += __shfl_xor_sync(0xffffffffu, p[j], o);
+      }
+      if (part == 0) {
+        float* op = out + ((size_t)(t0 + tt) * H + h) * vcols + c0 + cl0;
+#pragma unroll
+        for (int j = 0; j < CPT; ++j)
+          if (c0 + cl0 + j < vcols) op[j] = p[j];
+      }
     }
   }
-  if (active) {
+#pragma unroll
+  for (int j = 0; j < CPT; ++j)
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      if (e0 + i < dim) sp[e0 + i] = S[i];
-  }
+      if (c0 + cl0 + j < vcols && e0 + i < dim) sp[(size_t)(c0 + cl0 + j) * dim + e0 + i] = S[j][i];
 }
 
+template <typename T, int EPL, int CPT>
+static int launch_scan_as(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
+                          const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
+                          int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, int lpc, cudaStream_t s) {
+  const int cpb = kScanThreads / lpc * CPT;
+  const int vcols = vdim + ones_col;
+  const size_t smem = ((size_t)2 * kScanChunk * lpc * EPL + (size_t)kScanChunk * cpb + kScanChunk) * sizeof(float);
+  if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, EPL, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((vcols + cpb - 1) / cpb, H, R);
+  launch_kernel(decay_scan_kernel<T, EPL, CPT>, dim3(grid), dim3(kScanThreads), smem, s, 1, (const T*)q, (const T*)k, (const T*)v,
+                q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, H, kq_heads, dim, vdim, ones_col,
+                q_scale, lpc);
+  return launch_status();
+}
+
+// Four columns to a thread (they share the loads of k and q) where that still leaves a block for every SM; one otherwise.
+// A column's arithmetic is the same either way.
 template <typename T, int EPL>
 static int launch_scan(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride, const float* a,
                        const float* b, float* state, long slot_stride, const int* q_indptr, const int* state_slots, float* out,
                        int R, int H, int kq_heads, int dim, int vdim, int ones_col, float q_scale, cudaStream_t s) {
   int lpc = 1;
   while (lpc * EPL < dim) lpc <<= 1;
-  const int cpb = kScanThreads / lpc;
-  const int vcols = vdim + ones_col;
-  const size_t smem = ((size_t)2 * kScanChunk * dim + (size_t)kScanChunk * cpb + 2 * kScanChunk) * sizeof(float);
-  if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
-  if (smem > 40 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  dim3 grid((vcols + cpb - 1) / cpb, H, R);
-  launch_kernel(decay_scan_kernel<T, EPL>, dim3(grid), dim3(kScanThreads), smem, s, 1, (const T*)q, (const T*)k, (const T*)v, q_stride,
-                k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, H, kq_heads, dim, vdim, ones_col, q_scale, lpc);
-  return launch_status();
+  const int wide = kScanThreads / lpc * 4;
+  const long blocks_wide = (long)((vdim + ones_col + wide - 1) / wide) * H * R;
+  if (blocks_wide >= 148)
+    return launch_scan_as<T, EPL, 4>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
+                                     kq_heads, dim, vdim, ones_col, q_scale, lpc, s);
+  return launch_scan_as<T, EPL, 1>(q, k, v, q_stride, k_stride, v_stride, a, b, state, slot_stride, q_indptr, state_slots, out, R, H,
+                                   kq_heads, dim, vdim, ones_col, q_scale, lpc, s);
 }
 
 // q, k [T, kq_heads*dim] and v [T, H*vdim] in the activation type (row strides given); a, b float32 [T, H]; state: float32,
