@@ -75,6 +75,7 @@ _SIGNATURES = {
     "arle_scatter_tokens": [_P, _P, _P, _I, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "arle_dyt_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
+    "arle_gemm_heads_mma": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
     "arle_gemm_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_long, _I, _P],
     "arle_latent_prep": [_P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
@@ -1042,8 +1043,8 @@ def dyt_norm(resid, delta, rows, weight, bias, alpha: float, out, write_resid: b
 # ------------------------------------------------------------------ attention over latent vectors
 def gemm_heads(x, w, out) -> None:
     """out[m, h, :] = x[m, h, :] . w[h]^T for every head h: x [M, heads, K], w [heads, N, K] contiguous, out [M, heads, N].
-    x and out may be views into wider rows (any row stride and head stride, unit inner stride).  float32 sums with k
-    ascending in both precisions."""
+    x and out may be views into wider rows (any row stride and head stride, unit inner stride).  float32 sums; k ascending
+    in the general kernel, tensor-core tiles for bfloat16 rows on 16-byte boundaries (fast kernel set)."""
     M, heads, K = x.shape
     N = w.shape[1]
     if (w.shape[0] != heads or w.shape[2] != K or tuple(out.shape) != (M, heads, N) or not w.is_contiguous()
@@ -1051,6 +1052,12 @@ def gemm_heads(x, w, out) -> None:
         raise KernelError(f"gemm_heads: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     if x.dtype == torch.bfloat16 and w.dtype != torch.bfloat16:
         raise KernelError("gemm_heads: bfloat16 rows need bfloat16 matrices")
+    if (_KERNEL_SET == "fast" and x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        # the same sums on the tensor cores (tiles of 64 rows x 128 columns)
+        _check(library().arle_gemm_heads_mma(_ptr(x), _ptr(w), _ptr(out), M, N, K, heads, x.stride(0), K, out.stride(0), x.stride(1),
+                                             N * K, out.stride(1), _stream()), "gemm_heads_mma")
+        return
     _check(library().arle_gemm_heads(_ptr(x), _ptr(w), _ptr(out), _dt(x), _dt(w), M, N, K, heads, x.stride(0), K, out.stride(0),
                                      x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
 

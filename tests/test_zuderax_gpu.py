@@ -148,6 +148,20 @@ def test_latent_attention_kernels(dtype, H, dn, dr, rdims, rank, window, ps):
         assert ops.launch_count() - before == 4                          # both ran in parts and were merged
 
 
+@pytest.mark.parametrize("M,heads,K,N", [(1, 4, 32, 64), (8, 16, 64, 256), (70, 3, 128, 40), (300, 32, 512, 128), (129, 2, 24, 200)])
+def test_per_head_products_on_tensor_cores(M, heads, K, N):
+    """bfloat16 rows on 16-byte boundaries inside wider rows take the tensor-core tiles; against float64."""
+    g = torch.Generator().manual_seed(M + K)
+    wide = torch.randn(M, heads * (K + 8) + 16, generator=g).to(torch.bfloat16).to(DEV)
+    x = wide[:, 16: 16 + heads * (K + 8)].unflatten(1, (heads, K + 8))[:, :, :K]
+    w = (torch.randn(heads, N, K, generator=g) * K ** -0.5).to(torch.bfloat16).to(DEV)
+    out_wide = torch.zeros(M, heads, N + 5, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_heads(x, w, out_wide[:, :, :N])
+    want = torch.einsum("mhk,hnk->mhn", x.double().cpu(), w.double().cpu())
+    torch.testing.assert_close(out_wide[:, :, :N].double().cpu(), want, rtol=1e-2, atol=1e-2)
+    assert float(out_wide[:, :, N:].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,G,dim,vdim,ones", [(2, 2, 12, 20, True), (4, 2, 12, 8, False), (3, 1, 144, 16, False), (2, 2, 160, 32, True),
                                                (1, 1, 300, 5, True), (8, 1, 64, 64, False)])
