@@ -13,7 +13,7 @@
 //    (the per-expert twin of the plain product).  `rows` maps a place to its row of A (the token of the pair) or is
 //    absent (A is already in place order).
 //    In bfloat16 with aligned rows the same product runs on the tensor cores (moe_gemm_mma: tiles of 64 places x 128
-//    columns, mma.sync with float32 sums, operands brought in by cp.async in two stages), and a step of few pairs
+//    columns, mma.sync with float32 sums, operands brought in by cp.async in three stages), and a step of few pairs
 //    (decoding) runs it as one dot product a warp (moe_gemv: every chosen expert's rows are streamed once, 16 bytes
 //    a lane and load), since a tile of 64 places would be all but empty.
 //  * moe_combine: out[t] = sum_k weight[t, k] * Y[place(t, k)] (k ascending) + sigmoid(gate[t]) * shared[t].
@@ -202,10 +202,10 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
   }
 }
 
-constexpr int TM = 64, TN = 128, TK = 32, TPITCH = 40;
+constexpr int TM = 64, TN = 128, TK = 32, TPITCH = 40, kStages = 3;
 
 // A tile of 64 rows x 128 columns of C = A . W^T on the tensor cores: row r of the tile is row arow[r] of A (-1: none) and
-// row crow0 + r of C; M rows are live.  Two stages of cp.async, eight warps of 32 x 32, mma.sync with float32 sums.
+// row crow0 + r of C; M rows are live.  Three stages of cp.async, one barrier a stage, eight warps of 32 x 32, mma.sync with float32 sums.
 __device__ __forceinline__ void mma_tile_64x128(const __nv_bfloat16* __restrict__ A, int lda, const int* arow, const __nv_bfloat16* __restrict__ W,
                                                 int ldw, __nv_bfloat16* __restrict__ C, int ldc, size_t crow0, int M, int n0, int N, int K,
                                                 __nv_bfloat16 (*As)[TM * TPITCH], __nv_bfloat16 (*Ws)[TN * TPITCH]) {
@@ -234,16 +234,14 @@ __device__ __forceinline__ void mma_tile_64x128(const __nv_bfloat16* __restrict_
   const int nk = (K + TK - 1) / TK;
   load(0, 0);
   cp_commit();
+  if (nk > 1) load(1, TK);
+  cp_commit();
   for (int kt = 0; kt < nk; ++kt) {
-    const int st = kt & 1;
-    if (kt + 1 < nk) {
-      load(st ^ 1, (kt + 1) * TK);
-      cp_commit();
-      cp_wait<1>();
-    } else {
-      cp_wait<0>();
-    }
-    __syncthreads();
+    const int st = kt % kStages;
+    cp_wait<1>();                             // stage kt has landed (one younger group may still be under way)
+    __syncthreads();                          // and every warp has finished with the stage that is filled next
+    if (kt + 2 < nk) load((kt + 2) % kStages, (kt + 2) * TK);
+    cp_commit();
 #pragma unroll
     for (int kk = 0; kk < TK / 16; ++kk) {
       uint32_t a[2][4];
@@ -263,8 +261,8 @@ __device__ __forceinline__ void mma_tile_64x128(const __nv_bfloat16* __restrict_
         }
       }
     }
-    __syncthreads();
   }
+  cp_wait<0>();
   const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
@@ -291,8 +289,8 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const __nv_bfloat16* 
   if (tile >= plan[E + 1]) return;
   const int* tt = plan + E + 2 + 3 * tile;
   const int expert = tt[0], p0 = tt[1], M = tt[2];
-  __shared__ __align__(16) __nv_bfloat16 As[2][TM * TPITCH];
-  __shared__ __align__(16) __nv_bfloat16 Ws[2][TN * TPITCH];
+  __shared__ __align__(16) __nv_bfloat16 As[kStages][TM * TPITCH];
+  __shared__ __align__(16) __nv_bfloat16 Ws[kStages][TN * TPITCH];
   __shared__ int arow[TM];
   if (threadIdx.x < TM) arow[threadIdx.x] = (int)threadIdx.x < M ? (rows ? rows[p0 + threadIdx.x] : p0 + (int)threadIdx.x) : -1;
   __syncthreads();
@@ -306,8 +304,8 @@ __global__ void __launch_bounds__(256) gemm_heads_mma_kernel(const __nv_bfloat16
                                                              __nv_bfloat16* __restrict__ C, int ldc, int c_head, int M, int N, int K) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ __align__(16) __nv_bfloat16 As[2][TM * TPITCH];
-  __shared__ __align__(16) __nv_bfloat16 Ws[2][TN * TPITCH];
+  __shared__ __align__(16) __nv_bfloat16 As[kStages][TM * TPITCH];
+  __shared__ __align__(16) __nv_bfloat16 Ws[kStages][TN * TPITCH];
   __shared__ int arow[TM];
   const int m0 = blockIdx.y * TM, head = blockIdx.z;
   if (threadIdx.x < TM) arow[threadIdx.x] = m0 + (int)threadIdx.x < M ? m0 + (int)threadIdx.x : -1;
