@@ -129,9 +129,12 @@ class Scheduler:
     # ----------------------------------------------------------------- intake
     def max_request_tokens(self) -> int:
         """Most tokens one request may hold: the cache manager's per-request limit
-        and what the smallest cache group can hold at all."""
-        pool = min(self.cache.total_pages()) * self.cache.page_size
-        return min(self.cache.max_tokens_per_request, pool)
+        and what the smallest cache group can hold at all (a model without a paged cache, all of
+        whose mixers keep a state per request instead, has no such group)."""
+        pages = self.cache.total_pages()
+        if not pages:
+            return self.cache.max_tokens_per_request
+        return min(self.cache.max_tokens_per_request, min(pages) * self.cache.page_size)
 
     def add_request(self, rid, prompt: Sequence[int], params: SamplingParams = None) -> Request:
         params = params or SamplingParams()

@@ -18,7 +18,7 @@ from arle_b200.parts import build_model
 from arle_b200.sampling import SamplingParams
 from tiny_zuderax import CONFIGS, PAGE_SIZES, make_model_dir, read_model
 
-LENGTHS = {"Z1": [1, 5, 12, 23, 70, 33], "Z2": [2, 17, 40, 64, 9, 31], "S": [3, 30, 11, 2, 45]}
+LENGTHS = {"Z1": [1, 5, 12, 23, 70, 33], "Z2": [2, 17, 40, 64, 9, 31], "S": [3, 30, 11, 2, 45], "R": [1, 20, 33, 7]}
 F64 = torch.float64
 _cache = {}
 
@@ -172,12 +172,12 @@ def test_plain_window_sees_itself_and_the_tokens_before_it(tmp_path):
 
 # ------------------------------------------------------------------ the engine on the CPU
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
-@pytest.mark.parametrize("name", ["Z1", "Z2"])
+@pytest.mark.parametrize("name", ["Z1", "Z2", "R"])
 def test_cuttings_cpu(name, cut, tmp_path_factory, cpu_kernels):
     d, cfg, w, reqs, oracle = model_and_oracle(name, tmp_path_factory)
     steps = traces.mixed(reqs, seed=4) if cut == "mixed" else getattr(traces, cut)(reqs)
     ps = PAGE_SIZES[name]
-    runner = ModelRunner(load_model(d, torch.float32, "cpu"), ps, traces.peak_tokens(steps) // ps, 4, device="cpu")
+    runner = ModelRunner(load_model(d, torch.float32, "cpu"), ps, max(1, traces.peak_tokens(steps) // ps), 4, device="cpu")
     got = traces.run_trace(runner, steps)
     runner.cache.check()
     assert runner.cache.num_free_slots == 4 and all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups)
@@ -226,3 +226,16 @@ def test_greedy_generation_through_the_engine_and_scheduler(pages, tmp_path_fact
     if pages == 14:
         assert sum(o.preemptions for o in outs) > 0
     eng.runner.cache.check()
+
+
+def test_generation_with_a_model_that_keeps_no_paged_cache(tmp_path_factory, cpu_kernels):
+    """Recurrent mixers only: the cache manager has state slots and no page group; the scheduler admits by slots alone."""
+    d = make_model_dir("R", seed=3, root=str(tmp_path_factory.mktemp("gen")), sigma=0.3)
+    cfg, w = read_model(d)
+    prompts = [[5, 6, 7, 8], [9] * 12, [3], [100, 2, 50]]
+    eng = Engine(d, dtype="float32", device="cpu", page_size=4, num_pages=8, num_slots=2, chunked_prefill_size=8,
+                 max_num_batched_tokens=16, cuda_graph=False)
+    assert not eng.runner.cache.groups and len(eng.runner.cache.states) == 2
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    assert [o.token_ids for o in outs] == [plain.generate_greedy(cfg, w, p, 6) for p in prompts]
+

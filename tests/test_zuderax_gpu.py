@@ -36,7 +36,7 @@ IDS = ["f32", "bf16"]
 # from the exact result.
 REL = {torch.float32: 5e-4, torch.bfloat16: 1e-2}
 LENGTHS = {"Z1": [1, 5, 12, 23, 70, 130, 33], "Z2": [2, 17, 40, 96, 64, 31], "Z3": [3, 66, 150, 64, 40, 97], "S": [2, 33, 80, 17, 64],
-           "L": [3, 50, 64, 29]}
+           "L": [3, 50, 64, 29], "R": [1, 40, 33, 7, 70]}
 _cache, _rounding = {}, {}
 
 
@@ -277,7 +277,7 @@ def test_grouped_expert_products(dtype, T, E, top, K, N):
 # ------------------------------------------------------------------ the engine
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("name", ["Z1", "Z2", "Z3", "S", "L"])
+@pytest.mark.parametrize("name", ["Z1", "Z2", "Z3", "S", "L", "R"])
 def test_cuttings_gpu(name, dtype, cut, tmp_path_factory):
     d, cfg, w, reqs, oracle = model_and_oracle(name, tmp_path_factory)
     steps = traces.mixed(reqs, seed=4) if cut == "mixed" else getattr(traces, cut)(reqs)
@@ -429,7 +429,7 @@ def test_a_request_that_starts_again(dtype, tmp_path_factory):
 
 # ------------------------------------------------------------------ generation
 @pytest.mark.parametrize("graph", [True, False], ids=["graphs", "eager"])
-@pytest.mark.parametrize("name", ["F", "Z1"])
+@pytest.mark.parametrize("name", ["F", "Z1", "R"])
 def test_greedy_generation_equals_plain_model_f32(name, graph, tmp_path):
     d = make_model_dir(name, seed=3, root=str(tmp_path), sigma=0.3)
     cfg, w = read_model(d)
