@@ -72,7 +72,7 @@ TINY_F = model(180, 64, 1e-5, 1.0, [layer(latent(2, 16, 8, 8, 16, 24, 4000, 0.25
 TINY_S = model(180, 64, 1e-5, 1.0, [layer(mlstm(2, 16, 12, 12.0), dense(64)), layer(mamba(2, 12, 16, 1, 3, 2), None),
                                     layer(latent(2, 8, 8, 8, 8, 12, 5, 0.3), None)])
 # R: recurrent mixers only: a model without any paged cache
-TINY_R = model(150, 48, 1e-5, 1.0, [layer(mlstm(2, 8, 12, 5.0), dense(32)), layer(mamba(2, 8, 8, 1, 3, 1), None)])
+TINY_R = model(200, 48, 1e-5, 1.0, [layer(mlstm(2, 8, 12, 5.0), dense(32)), layer(mamba(2, 8, 8, 1, 3, 1), None)])
 CONFIGS = {"R": TINY_R, "Z1": TINY_Z1, "Z2": TINY_Z2, "Z3": TINY_Z3, "L": TINY_L, "F": TINY_F, "S": TINY_S}
 INIT = {"R": dict(sigma=0.2, gain_jitter=0.3), "Z1": dict(sigma=0.12, gain_jitter=0.3), "Z2": dict(sigma=0.14, gain_jitter=0.3), "Z3": dict(sigma=0.06, gain_jitter=0.3),
         "L": dict(sigma=0.12, gain_jitter=0.3), "F": dict(sigma=0.12, gain_jitter=0.3), "S": dict(sigma=0.12, gain_jitter=0.3)}
