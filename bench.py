@@ -169,10 +169,10 @@ ZUDERAX_SIZES = {"0.6b": dict(heads=16, dim=64, rot=32, vdim=64, rank=256, lstm=
 def zuderax_config(z, zz, L, window):
     ff = {"kind": "dense", "ff": z["ff"]}
     routed = {"kind": "moe", "expert": {"ff": z["ff"] // zz["top"]}, "shared": {"ff": z["ff"] // zz["top"]},
-              "router": {"experts": zz["experts"], "top": zz["top"], "scale": 2.5, "groups": {"count": zz["groups"], "keep": zz["keep"]}}}
+              "router": {"experts": zz["experts"], "top": zz["top"], "scale": 2.0, "groups": {"count": zz["groups"], "keep": zz["keep"]}}}
     mixers = [("latent_attention", {"heads": zz["heads"], "dim": zz["dim"], "rot_dim": zz["rot"], "vdim": zz["vdim"], "kv_rank": zz["rank"],
                                     "scale": (zz["dim"] + zz["rot"]) ** -0.5, "mask": {"size": window}, "rot": {"base": 1e6, "dims": zz["rot"]}}),
-              ("mlstm", {"heads": zz["lstm"][0], "dim": zz["lstm"][1], "vdim": zz["lstm"][2], "gate_cap": 15.0}),
+              ("mlstm", {"heads": zz["lstm"][0], "dim": zz["lstm"][1], "vdim": zz["lstm"][2], "gate_cap": 10.0}),
               ("mamba2", {"heads": zz["ssm"][0], "vdim": zz["ssm"][1], "state": zz["ssm"][2], "groups": zz["ssm"][3], "conv": 4, "norm_groups": 1})]
     layers = [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1], "mlp": routed if i % 2 else ff} for i in range(L)]
     return {"architecture": "Zuderax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
